@@ -1,0 +1,157 @@
+"""ctypes binding of libkb200.so (C ABI in csrc/include/kb200.h).
+
+The library is built in-tree by ``kernel_b200.csrc.build``.  Loading never
+falls back silently: on a machine with a GPU a missing library is an error,
+because every fused op must run its hand-written kernel there.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+KB_MAX_WORLD = 16
+
+KB_OK, KB_ERR_CUDA, KB_ERR_ARG, KB_ERR_TIMEOUT, KB_ERR_IO, KB_ERR_UNSUPPORTED = range(6)
+BACKEND_HOST, BACKEND_VMM, BACKEND_IPC = 0, 1, 2
+GEMM_PLAIN, GEMM_RS, GEMM_AG = 0, 1, 2
+
+DEV_CODES = {0: "ok", 1: "pipeline barrier timeout", 2: "peer flag timeout", 3: "index out of bounds"}
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libkb200.so"
+
+
+class NativeError(RuntimeError):
+    """A call into libkb200 returned a non-zero status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"libkb200 status {code}: {message}")
+        self.code = code
+
+
+class SymmTimeoutError(NativeError):
+    """A rendezvous step or a device-side wait ran out of time."""
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("mode", C.c_int),
+        ("M", C.c_int),
+        ("N", C.c_int),
+        ("K", C.c_int),
+        ("A", C.c_void_p),
+        ("B", C.c_void_p),
+        ("bias", C.c_void_p),
+        ("bias_scale", C.c_float),
+        ("out", C.c_void_p),
+        ("rank", C.c_int),
+        ("world", C.c_int),
+        ("epoch", C.c_uint32),
+        ("peer_base", C.c_void_p * KB_MAX_WORLD),
+        ("data_off", C.c_uint64),
+        ("flag_off", C.c_uint64),
+        ("counter_off", C.c_uint64),
+        ("status", C.c_void_p),
+        ("wait_limit_ns", C.c_uint64),
+        ("num_ctas", C.c_int),
+    ]
+
+
+class A2aArgs(C.Structure):
+    _fields_ = [
+        ("rank", C.c_int),
+        ("world", C.c_int),
+        ("num_experts", C.c_int),
+        ("topk", C.c_int),
+        ("hidden", C.c_int),
+        ("max_tokens", C.c_int),
+        ("num_tokens", C.c_int),
+        ("elem_bytes", C.c_int),
+        ("dtype", C.c_int),
+        ("x", C.c_void_p),
+        ("indices", C.c_void_p),
+        ("weights", C.c_void_p),
+        ("out", C.c_void_p),
+        ("slots", C.c_void_p),
+        ("epoch", C.c_uint32),
+        ("peer_base", C.c_void_p * KB_MAX_WORLD),
+        ("recv_off", C.c_uint64),
+        ("y_off", C.c_uint64),
+        ("count_off", C.c_uint64),
+        ("flag_off", C.c_uint64),
+        ("sync_off", C.c_uint64),
+        ("scale_mode", C.c_int),
+        ("status", C.c_void_p),
+        ("wait_limit_ns", C.c_uint64),
+        ("num_ctas", C.c_int),
+    ]
+
+
+_lib = None
+
+
+def _declare(lib: C.CDLL) -> None:
+    vp, i, u32, u64 = C.c_void_p, C.c_int, C.c_uint32, C.c_uint64
+    sig = {
+        "kb_last_error": (C.c_char_p, []),
+        "kb_fd_allgather": (i, [C.c_char_p, C.c_char_p, i, i, i, C.POINTER(i), i]),
+        "kb_symm_create": (i, [i, i, i, u64, i, C.POINTER(vp)]),
+        "kb_symm_segment_bytes": (u64, [vp]),
+        "kb_symm_local_fd": (i, [vp]),
+        "kb_symm_ipc_handle": (i, [vp, vp]),
+        "kb_symm_map_peers": (i, [vp, C.POINTER(i), vp]),
+        "kb_symm_peer_ptr": (vp, [vp, i]),
+        "kb_symm_local_ptr": (vp, [vp]),
+        "kb_symm_mc_supported": (i, [i]),
+        "kb_symm_mc_create": (i, [vp, C.POINTER(i)]),
+        "kb_symm_mc_join": (i, [vp, i]),
+        "kb_symm_mc_bind": (i, [vp]),
+        "kb_symm_mc_ptr": (vp, [vp]),
+        "kb_symm_destroy": (i, [vp]),
+        "kb_symm_host_barrier": (i, [vp, u64, u32, i]),
+        "kb_wait_flags": (i, [vp, i, u32, u64, vp, vp]),
+        "kb_device_barrier": (i, [C.POINTER(vp), u64, i, i, u32, u64, vp, vp]),
+        "kb_gemm": (i, [C.POINTER(GemmArgs), vp]),
+        "kb_gemm_rs_data_bytes": (u64, [i, i, i]),
+        "kb_gemm_rs_flag_bytes": (u64, [i, i, i]),
+        "kb_gemm_ag_data_bytes": (u64, [i, i]),
+        "kb_gemm_ag_flag_bytes": (u64, [i, i]),
+        "kb_gemm_ag_counter_bytes": (u64, [i, i]),
+        "kb_a2a_rows_bytes": (u64, [i, i, i, i, i]),
+        "kb_a2a_dispatch": (i, [C.POINTER(A2aArgs), vp]),
+        "kb_a2a_expert_scale": (i, [C.POINTER(A2aArgs), vp]),
+        "kb_a2a_combine": (i, [C.POINTER(A2aArgs), vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+
+
+def available() -> bool:
+    return LIB_PATH.exists()
+
+
+def lib() -> C.CDLL:
+    """Returns the loaded library, building it first if the file is missing."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            from .csrc.build import build
+
+            build()
+        _lib = C.CDLL(str(LIB_PATH))
+        _declare(_lib)
+    return _lib
+
+
+def last_error() -> str:
+    return (lib().kb_last_error() or b"").decode(errors="replace")
+
+
+def check(code: int) -> None:
+    if code == KB_OK:
+        return
+    msg = last_error()
+    if code == KB_ERR_TIMEOUT:
+        raise SymmTimeoutError(code, msg)
+    raise NativeError(code, msg)

@@ -1,0 +1,97 @@
+"""Build libkb200.so in-tree with nvcc for sm_100a.
+
+The library has a plain C ABI (see include/kb200.h) and depends on nothing but
+the statically linked CUDA runtime, so it builds on a machine without a GPU and
+loads on a machine without a driver.
+
+    python -m kernel_b200.csrc.build [--force] [--verbose]
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent
+LIB_DIR = CSRC.parent / "lib"
+LIB_PATH = LIB_DIR / "libkb200.so"
+OBJ_DIR = CSRC / "build"
+
+SOURCES = [
+    "common/host_util.cpp",
+    "symm/fd_exchange.cpp",
+    "symm/symm_heap.cpp",
+    "kernels/a2a.cu",
+    "kernels/gemm_sm100.cu",
+]
+
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-x", "cu"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found (set NVCC=/path/to/nvcc)")
+
+
+def _sources() -> list[str]:
+    srcs = list(SOURCES)
+    for extra in sorted((CSRC / "kernels").glob("*.cu")):
+        rel = str(extra.relative_to(CSRC))
+        if rel not in srcs:
+            srcs.append(rel)
+    return srcs
+
+
+def _digest() -> str:
+    h = hashlib.sha256()
+    files = sorted(p for p in CSRC.rglob("*") if p.suffix in {".cu", ".cuh", ".cpp", ".h", ".py"} and "build/" not in str(p))
+    for p in files:
+        h.update(str(p.relative_to(CSRC)).encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every source for sm_100a and link libkb200.so; returns its path."""
+    LIB_DIR.mkdir(exist_ok=True)
+    OBJ_DIR.mkdir(exist_ok=True)
+    stamp = OBJ_DIR / "digest.txt"
+    digest = _digest()
+    if not force and LIB_PATH.exists() and stamp.exists() and stamp.read_text() == digest:
+        return LIB_PATH
+    nvcc = _nvcc()
+
+    def compile_one(rel: str) -> Path:
+        src = CSRC / rel
+        obj = OBJ_DIR / (rel.replace("/", "_") + ".o")
+        cmd = [nvcc, *ARCH_FLAGS, *COMMON, "-I", str(CSRC / "include"), "-c", str(src), "-o", str(obj)]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose or res.returncode != 0:
+            sys.stderr.write(f"$ {' '.join(cmd)}\n{res.stdout}{res.stderr}\n")
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {rel}")
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as pool:
+        objs = list(pool.map(compile_one, _sources()))
+    link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-cudart", "static", "-lpthread", "-ldl", "-lrt"]
+    res = subprocess.run(link, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(f"$ {' '.join(link)}\n{res.stdout}{res.stderr}\n")
+        raise RuntimeError("link failed")
+    stamp.write_text(digest)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    print(path)

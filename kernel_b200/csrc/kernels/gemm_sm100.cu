@@ -1,0 +1,652 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a with three epilogues:
+//
+//   PLAIN  out = A * B^T (+ bias)
+//   RS     GEMM fused with reduce-scatter: every 128x256 tile is converted to
+//          bf16 as it retires and its rows are stored straight into the row
+//          owner's staging area over NVLink; the owner's own tiles run last
+//          and their epilogue sums the peers' partials in fp32, adds the bias
+//          and writes the output shard.  No collective library call, no
+//          second kernel.
+//   AG     all-gather fused with GEMM: extra "comm" warps of the same kernel
+//          stream this rank's A rows into every peer's gather buffer while the
+//          tensor cores already work on the rows that are present; the TMA
+//          producer waits (bounded) on a per-row-block flag before it loads
+//          rows that come from a peer.
+//
+// Mainloop: one TMA producer thread fills a 4-stage ring of 128x64 (A) and
+// 256x64 (B) K-major tiles with 128-byte swizzle; one thread issues
+// tcgen05.mma (M128 N256 K16) into one of two 256-column TMEM accumulators;
+// four epilogue warps drain the other accumulator (tcgen05.ld -> bf16 ->
+// swizzled smem -> 16-byte row-contiguous global accesses).
+//
+// The op replaces torch.matmul + bias add + reduce_scatter_tensor of the
+// reference (gemm_rs/reference.py:49-60, gemm_rs/submission.py:23-28).
+//
+// TMA loads here are plain single-CTA loads from this GPU's own memory.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../common/host_util.h"
+#include "../common/ptx.cuh"
+#include "../include/kb200.h"
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int EPI_COLS = 128;                 // columns staged per epilogue pass
+constexpr int EPI_ROW_BYTES = EPI_COLS * 2;   // 256
+constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;
+constexpr int EPI_BYTES = 4 * EPI_WARP_BYTES;
+constexpr int TMEM_COLS = 512;
+constexpr int BAR_BYTES = 256;
+constexpr int SMEM_BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + EPI_BYTES + BAR_BYTES;
+constexpr int THREADS_BASE = 256;             // warps 0..3 control, 4..7 epilogue
+constexpr int THREADS_AG = 384;               // + warps 8..11 comm
+
+struct alignas(64) GemmParams {
+  CUtensorMap tmA;
+  CUtensorMap tmB;
+  int mode, M, N, K;
+  int MB, NB, KB;
+  const bf16* bias;
+  float bias_scale;
+  bf16* out;
+  int rank, world, rpo;
+  uint32_t epoch;
+  char* peer_base[KB_MAX_WORLD];
+  uint64_t data_off, flag_off, counter_off;
+  const bf16* a_local;
+  uint32_t* status;
+  uint64_t limit_ns;
+  int own_lo_mb, own_hi_mb;
+  int ag_parts;
+};
+
+enum Site : uint32_t {
+  SITE_PROD_EMPTY = 1,
+  SITE_MMA_FULL = 2,
+  SITE_MMA_TEMPTY = 3,
+  SITE_EPI_TFULL = 4,
+  SITE_RS_FLAG = 5,
+  SITE_AG_FLAG = 6,
+};
+
+struct Smem {
+  uint8_t* a;
+  uint8_t* b;
+  uint8_t* epi;
+  uint64_t* full;
+  uint64_t* empty;
+  uint64_t* tfull;
+  uint64_t* tempty;
+  uint32_t* tmem_slot;
+  volatile uint32_t* abort;
+};
+
+__device__ __forceinline__ Smem carve(uint8_t* raw) {
+  Smem s;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  s.a = base;
+  s.b = base + STAGES * A_BYTES;
+  s.epi = s.b + STAGES * B_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s.epi + EPI_BYTES);
+  s.full = bars;
+  s.empty = bars + STAGES;
+  s.tfull = bars + 2 * STAGES;
+  s.tempty = bars + 2 * STAGES + 2;
+  s.tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  s.abort = s.tmem_slot + 1;
+  return s;
+}
+
+// Position in this CTA's static schedule -> tile coordinates.  Row blocks are
+// visited in a rank-rotated order: RS starts just after the blocks this rank
+// owns (so they come last and every owner is fed by a different peer at any
+// time); AG starts with this rank's own rows (which need no transfer).
+__device__ __forceinline__ void tile_at(const GemmParams& p, int pos, int& mb, int& nb) {
+  int j = pos / p.NB;
+  nb = pos - j * p.NB;
+  int start = 0;
+  if (p.mode == KB_GEMM_RS) start = p.own_hi_mb + 1;
+  if (p.mode == KB_GEMM_AG) start = p.own_lo_mb;
+  mb = (start + j) % p.MB;
+}
+
+__device__ __forceinline__ uint32_t* rs_flag(const GemmParams& p, int on_rank, int src, int tile) {
+  const uint32_t parity = p.epoch & 1u;
+  uint32_t* base = reinterpret_cast<uint32_t*>(p.peer_base[on_rank] + p.flag_off);
+  return base + (static_cast<size_t>(parity) * p.world + src) * (static_cast<size_t>(p.MB) * p.NB) + tile;
+}
+__device__ __forceinline__ bf16* rs_stage_row(const GemmParams& p, int on_rank, int src, int row_local) {
+  const uint32_t parity = p.epoch & 1u;
+  bf16* base = reinterpret_cast<bf16*>(p.peer_base[on_rank] + p.data_off);
+  return base + ((static_cast<size_t>(parity) * p.world + src) * p.rpo + row_local) * static_cast<size_t>(p.N);
+}
+__device__ __forceinline__ uint32_t* ag_flag(const GemmParams& p, int on_rank, int src, int mb) {
+  const uint32_t parity = p.epoch & 1u;
+  uint32_t* base = reinterpret_cast<uint32_t*>(p.peer_base[on_rank] + p.flag_off);
+  return base + (static_cast<size_t>(parity) * p.world + src) * p.MB + mb;
+}
+__device__ __forceinline__ bf16* ag_gather_row(const GemmParams& p, int on_rank, int row) {
+  const uint32_t parity = p.epoch & 1u;
+  bf16* base = reinterpret_cast<bf16*>(p.peer_base[on_rank] + p.data_off);
+  return base + (static_cast<size_t>(parity) * p.M + row) * static_cast<size_t>(p.K);
+}
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void comm_bar_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
+// TMEM -> bf16 -> this warp's 32 x 128 staging rows (16-byte chunks XOR-swizzled
+// by row so both the row-per-thread writes and the row-contiguous reads are
+// bank-conflict free).
+__device__ __forceinline__ void stage_half(uint32_t taddr, uint8_t* warp_epi, int lane) {
+#pragma unroll
+  for (int c = 0; c < EPI_COLS / 32; ++c) {
+    uint32_t r[32];
+    kb::tmem_ld_32x32(taddr + c * 32, r);
+    kb::tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 v;
+      v.x = kb::pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+      v.y = kb::pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+      v.z = kb::pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+      v.w = kb::pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+      const int j = c * 4 + i;
+      const int phys = j ^ (lane & 15);
+      *reinterpret_cast<uint4*>(warp_epi + lane * EPI_ROW_BYTES + phys * 16) = v;
+    }
+  }
+}
+
+template <bool kAG>
+__global__ void __launch_bounds__(kAG ? THREADS_AG : THREADS_BASE, 1)
+gemm_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem sm = carve(smem_raw);
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int total_tiles = p.MB * p.NB;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      kb::mbar_init(&sm.full[s], 1);
+      kb::mbar_init(&sm.empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      kb::mbar_init(&sm.tfull[a], 1);
+      kb::mbar_init(&sm.tempty[a], 4);
+    }
+    *sm.abort = 0;
+    kb::mbar_fence_init();
+  }
+  if (warp == 2) {
+    kb::tmem_alloc(sm.tmem_slot, TMEM_COLS);
+    kb::tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    kb::tma_prefetch_desc(&p.tmA);
+    kb::tma_prefetch_desc(&p.tmB);
+  }
+  kb::tc_fence_before_sync();
+  __syncthreads();
+  kb::tc_fence_after_sync();
+  const uint32_t tmem_base = *sm.tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer ----
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      int ready_mb = -1;
+      bool ok = true;
+      for (int pos = blockIdx.x; pos < total_tiles && ok; pos += gridDim.x) {
+        int mb, nb;
+        tile_at(p, pos, mb, nb);
+        if (kAG && mb != ready_mb) {
+          const int s_lo = (mb * BM) / p.rpo;
+          int last_row = mb * BM + BM - 1;
+          if (last_row > p.M - 1) last_row = p.M - 1;
+          const int s_hi = last_row / p.rpo;
+          for (int src = s_lo; src <= s_hi; ++src) {
+            if (!kb::wait_flag_ge(ag_flag(p, p.rank, src, mb), p.epoch, p.limit_ns)) {
+              kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_AG_FLAG, (uint32_t)src, p.epoch);
+            }
+          }
+          kb::fence_proxy_async_global();
+          ready_mb = mb;
+        }
+        for (int kb_i = 0; kb_i < p.KB; ++kb_i) {
+          if (!kb::mbar_wait_bounded(&sm.empty[s], ph ^ 1u, p.limit_ns)) {
+            kb::report_status(p.status, KB_DEV_TIMEOUT_MBAR, SITE_PROD_EMPTY, (uint32_t)pos, p.epoch);
+            *sm.abort = 1;
+            ok = false;
+            break;
+          }
+          kb::mbar_arrive_expect_tx(&sm.full[s], A_BYTES + B_BYTES);
+          kb::tma_load_2d(sm.a + s * A_BYTES, &p.tmA, &sm.full[s], kb_i * BK, mb * BM);
+          kb::tma_load_2d(sm.b + s * B_BYTES, &p.tmB, &sm.full[s], kb_i * BK, nb * BN);
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // -------------------------------------------------------- MMA issuer ----
+    if (lane == 0) {
+      constexpr uint32_t idesc = kb::umma_idesc_bf16(BM, BN);
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int pos = blockIdx.x; pos < total_tiles && ok; pos += gridDim.x, ++it) {
+        const uint32_t acc = it & 1u;
+        const uint32_t aph = (it >> 1) & 1u;
+        if (!kb::mbar_wait_bounded(&sm.tempty[acc], aph ^ 1u, p.limit_ns)) {
+          kb::report_status(p.status, KB_DEV_TIMEOUT_MBAR, SITE_MMA_TEMPTY, (uint32_t)pos, p.epoch);
+          *sm.abort = 1;
+          break;
+        }
+        kb::tc_fence_after_sync();
+        const uint32_t d = tmem_base + acc * BN;
+        for (int kb_i = 0; kb_i < p.KB; ++kb_i) {
+          if (!kb::mbar_wait_bounded(&sm.full[s], ph, p.limit_ns)) {
+            kb::report_status(p.status, KB_DEV_TIMEOUT_MBAR, SITE_MMA_FULL, (uint32_t)pos, p.epoch);
+            *sm.abort = 1;
+            ok = false;
+            break;
+          }
+          kb::tc_fence_after_sync();
+          const uint32_t a_addr = kb::smem_u32(sm.a + s * A_BYTES);
+          const uint32_t b_addr = kb::smem_u32(sm.b + s * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            kb::umma_f16(d, kb::umma_desc_k_sw128(a_addr + k * UMMA_K * 2), kb::umma_desc_k_sw128(b_addr + k * UMMA_K * 2),
+                         idesc, (kb_i | k) != 0 ? 1u : 0u);
+          }
+          kb::umma_commit(&sm.empty[s]);
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (ok) kb::umma_commit(&sm.tfull[acc]);
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 4 && warp < 8) {
+    // ---------------------------------------------------------- epilogue ----
+    const int q = warp - 4;
+    const int et = tid - 128;
+    uint8_t* warp_epi = sm.epi + q * EPI_WARP_BYTES;
+    const bool rs = (p.mode == KB_GEMM_RS) && p.world > 1;
+    uint32_t it = 0;
+    for (int pos = blockIdx.x; pos < total_tiles; pos += gridDim.x, ++it) {
+      int mb, nb;
+      tile_at(p, pos, mb, nb);
+      const uint32_t acc = it & 1u;
+      const uint32_t aph = (it >> 1) & 1u;
+      if (!kb::mbar_wait_bounded(&sm.tfull[acc], aph, p.limit_ns)) {
+        kb::report_status(p.status, KB_DEV_TIMEOUT_MBAR, SITE_EPI_TFULL, (uint32_t)pos, p.epoch);
+        *sm.abort = 1;
+        break;
+      }
+      kb::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      const int row0 = mb * BM;
+      int last_row = row0 + BM - 1;
+      if (last_row > p.M - 1) last_row = p.M - 1;
+      int o_lo = 0, o_hi = 0;
+      bool has_remote = false, has_own = true;
+      if (rs) {
+        o_lo = row0 / p.rpo;
+        o_hi = last_row / p.rpo;
+        has_own = (p.rank >= o_lo && p.rank <= o_hi);
+        has_remote = !(o_lo == p.rank && o_hi == p.rank);
+      }
+      const int tile_id = mb * p.NB + nb;
+      bool released = false;
+
+      if (has_remote) {
+        // Phase A: rows that belong to other ranks go to their owners.
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          stage_half(taddr + h * EPI_COLS, warp_epi, lane);
+          if (h == 1 && !has_own) {
+            kb::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) kb::mbar_arrive(&sm.tempty[acc]);
+            released = true;
+          }
+          __syncwarp();
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int row = i * 2 + (lane >> 4);
+            const int j = lane & 15;
+            const int gr = row0 + q * 32 + row;
+            const int col = nb * BN + h * EPI_COLS + j * 8;
+            if (gr < p.M && col < p.N) {
+              const int owner = gr / p.rpo;
+              if (owner != p.rank) {
+                const uint4 v = *reinterpret_cast<const uint4*>(warp_epi + row * EPI_ROW_BYTES + ((j ^ (row & 15)) * 16));
+                bf16* dst = rs_stage_row(p, owner, p.rank, gr - owner * p.rpo) + col;
+                kb::st_sys_v4(dst, v);
+              }
+            }
+          }
+          __syncwarp();
+        }
+        epi_bar_sync();
+        if (et == 0) {
+          kb::fence_sys();
+          for (int o = o_lo; o <= o_hi; ++o) {
+            if (o != p.rank) kb::st_release_sys_u32(rs_flag(p, o, p.rank, tile_id), p.epoch);
+          }
+        }
+      }
+
+      if (has_own) {
+        if (rs) {
+          if (et < p.world && et != p.rank) {
+            if (!kb::wait_flag_ge(rs_flag(p, p.rank, et, tile_id), p.epoch, p.limit_ns)) {
+              kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_RS_FLAG, (uint32_t)et, p.epoch);
+            }
+          }
+          epi_bar_sync();
+        }
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          stage_half(taddr + h * EPI_COLS, warp_epi, lane);
+          if (h == 1) {
+            kb::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) kb::mbar_arrive(&sm.tempty[acc]);
+            released = true;
+          }
+          __syncwarp();
+#pragma unroll 2
+          for (int i = 0; i < 16; ++i) {
+            const int row = i * 2 + (lane >> 4);
+            const int j = lane & 15;
+            const int gr = row0 + q * 32 + row;
+            const int col = nb * BN + h * EPI_COLS + j * 8;
+            if (gr < p.M && col < p.N) {
+              int out_row = gr;
+              bool mine = true;
+              if (rs) {
+                const int owner = gr / p.rpo;
+                mine = (owner == p.rank);
+                out_row = gr - p.rank * p.rpo;
+              }
+              if (mine) {
+                const uint4 v = *reinterpret_cast<const uint4*>(warp_epi + row * EPI_ROW_BYTES + ((j ^ (row & 15)) * 16));
+                float f[8];
+                {
+                  float2 t;
+                  t = kb::unpack_bf16x2(v.x); f[0] = t.x; f[1] = t.y;
+                  t = kb::unpack_bf16x2(v.y); f[2] = t.x; f[3] = t.y;
+                  t = kb::unpack_bf16x2(v.z); f[4] = t.x; f[5] = t.y;
+                  t = kb::unpack_bf16x2(v.w); f[6] = t.x; f[7] = t.y;
+                }
+                if (rs) {
+                  // Fixed summation order over sources keeps the result
+                  // bit-reproducible from run to run.
+                  for (int src = 0; src < p.world; ++src) {
+                    if (src == p.rank) continue;
+                    const uint4 u = kb::ld_sys_v4(rs_stage_row(p, p.rank, src, out_row) + col);
+                    float2 t;
+                    t = kb::unpack_bf16x2(u.x); f[0] += t.x; f[1] += t.y;
+                    t = kb::unpack_bf16x2(u.y); f[2] += t.x; f[3] += t.y;
+                    t = kb::unpack_bf16x2(u.z); f[4] += t.x; f[5] += t.y;
+                    t = kb::unpack_bf16x2(u.w); f[6] += t.x; f[7] += t.y;
+                  }
+                }
+                if (p.bias != nullptr) {
+                  const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+                  float2 t;
+                  t = kb::unpack_bf16x2(bv.x); f[0] += p.bias_scale * t.x; f[1] += p.bias_scale * t.y;
+                  t = kb::unpack_bf16x2(bv.y); f[2] += p.bias_scale * t.x; f[3] += p.bias_scale * t.y;
+                  t = kb::unpack_bf16x2(bv.z); f[4] += p.bias_scale * t.x; f[5] += p.bias_scale * t.y;
+                  t = kb::unpack_bf16x2(bv.w); f[6] += p.bias_scale * t.x; f[7] += p.bias_scale * t.y;
+                }
+                uint4 o;
+                o.x = kb::pack_bf16x2(f[0], f[1]);
+                o.y = kb::pack_bf16x2(f[2], f[3]);
+                o.z = kb::pack_bf16x2(f[4], f[5]);
+                o.w = kb::pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(out_row) * p.N + col) = o;
+              }
+            }
+          }
+          __syncwarp();
+        }
+      }
+      if (!released) {
+        kb::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) kb::mbar_arrive(&sm.tempty[acc]);
+      }
+    }
+  } else if (kAG && warp >= 8) {
+    // -------------------------------------------------- all-gather pusher ----
+    const int ct = tid - 256;
+    const int n_chunks = p.own_hi_mb - p.own_lo_mb + 1;
+    const int parts = p.ag_parts;
+    const int total_tasks = p.world * n_chunks * parts;
+    const int own_row0 = p.rank * p.rpo;
+    uint32_t* counters = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.counter_off);
+    for (int t = blockIdx.x; t < total_tasks; t += gridDim.x) {
+      const int dj = t / (n_chunks * parts);
+      const int rem = t - dj * (n_chunks * parts);
+      const int c = rem / parts;
+      const int part = rem - c * parts;
+      const int dst = (p.rank - dj + p.world) % p.world;
+      const int mb = p.own_lo_mb + c;
+      int r_begin = mb * BM;
+      if (r_begin < own_row0) r_begin = own_row0;
+      int r_end = mb * BM + BM;
+      if (r_end > own_row0 + p.rpo) r_end = own_row0 + p.rpo;
+      if (r_end > p.M) r_end = p.M;
+      const int rows = r_end - r_begin;
+      const int per = (rows + parts - 1) / parts;
+      int rb = r_begin + part * per;
+      int re = rb + per;
+      if (re > r_end) re = r_end;
+      if (rb < re) {
+        const size_t nvec = static_cast<size_t>(re - rb) * p.K / 8;
+        const uint4* src = reinterpret_cast<const uint4*>(p.a_local + static_cast<size_t>(rb - own_row0) * p.K);
+        uint4* dstp = reinterpret_cast<uint4*>(ag_gather_row(p, dst, rb));
+        size_t v = ct;
+        for (; v + 3 * 128 < nvec; v += 4 * 128) {
+          const uint4 x0 = kb::ld_nc_v4(src + v);
+          const uint4 x1 = kb::ld_nc_v4(src + v + 128);
+          const uint4 x2 = kb::ld_nc_v4(src + v + 256);
+          const uint4 x3 = kb::ld_nc_v4(src + v + 384);
+          kb::st_sys_v4(dstp + v, x0);
+          kb::st_sys_v4(dstp + v + 128, x1);
+          kb::st_sys_v4(dstp + v + 256, x2);
+          kb::st_sys_v4(dstp + v + 384, x3);
+        }
+        for (; v < nvec; v += 128) kb::st_sys_v4(dstp + v, kb::ld_nc_v4(src + v));
+      }
+      comm_bar_sync();
+      if (ct == 0) {
+        kb::fence_sys();
+        const uint32_t old = atomicAdd(&counters[dst * n_chunks + c], 1u);
+        if ((old + 1u) % static_cast<uint32_t>(parts) == 0u) {
+          kb::fence_sys();
+          kb::st_release_sys_u32(ag_flag(p, dst, p.rank, mb), p.epoch);
+        }
+      }
+    }
+  }
+
+  kb::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    kb::tc_fence_after_sync();
+    kb::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host ----
+int make_tmap(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  auto encode = KB_DRV(cuTensorMapEncodeTiled);
+  if (encode == nullptr) return KB_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    kb::set_error("cuTensorMapEncodeTiled failed: CUresult %d (ptr %p rows %llu cols %llu)", (int)r, ptr,
+                  (unsigned long long)rows, (unsigned long long)cols);
+    return KB_ERR_CUDA;
+  }
+  return KB_OK;
+}
+
+inline uint64_t round_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+extern "C" uint64_t kb_gemm_rs_data_bytes(int M, int N, int world) {
+  return round_up(2ull * world * (uint64_t)(M / world) * N * 2, 256);
+}
+extern "C" uint64_t kb_gemm_rs_flag_bytes(int M, int N, int world) {
+  const uint64_t tiles = (uint64_t)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return round_up(2ull * world * tiles * 4, 256);
+}
+extern "C" uint64_t kb_gemm_ag_data_bytes(int M, int K) { return round_up(2ull * (uint64_t)M * K * 2, 256); }
+extern "C" uint64_t kb_gemm_ag_flag_bytes(int M, int world) {
+  return round_up(2ull * world * ((M + BM - 1) / BM) * 4, 256);
+}
+extern "C" uint64_t kb_gemm_ag_counter_bytes(int M, int world) {
+  return round_up((uint64_t)world * ((M + BM - 1) / BM + 1) * 4, 256);
+}
+
+extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (a == nullptr) return KB_ERR_ARG;
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0 || (a->K % 8) != 0 || (a->N % 8) != 0) {
+    kb::set_error("kb_gemm: need M,N,K > 0 and N,K multiples of 8 (got %d %d %d)", a->M, a->N, a->K);
+    return KB_ERR_ARG;
+  }
+  if (a->world < 1 || a->world > KB_MAX_WORLD || a->rank < 0 || a->rank >= a->world) {
+    kb::set_error("kb_gemm: bad rank/world %d/%d", a->rank, a->world);
+    return KB_ERR_ARG;
+  }
+  auto misaligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
+  if (misaligned(a->A) || misaligned(a->B) || misaligned(a->out) || (a->bias && misaligned(a->bias))) {
+    kb::set_error("kb_gemm: operand pointers must be 16-byte aligned");
+    return KB_ERR_ARG;
+  }
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.mode = a->mode;
+  p.M = a->M;
+  p.N = a->N;
+  p.K = a->K;
+  p.MB = (a->M + BM - 1) / BM;
+  p.NB = (a->N + BN - 1) / BN;
+  p.KB = (a->K + BK - 1) / BK;
+  p.bias = static_cast<const bf16*>(a->bias);
+  p.bias_scale = a->bias_scale;
+  p.out = static_cast<bf16*>(a->out);
+  p.rank = a->rank;
+  p.world = a->world;
+  p.epoch = a->epoch;
+  p.status = a->status;
+  p.limit_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
+  p.data_off = a->data_off;
+  p.flag_off = a->flag_off;
+  p.counter_off = a->counter_off;
+  p.ag_parts = 8;
+  for (int r = 0; r < a->world; ++r) p.peer_base[r] = static_cast<char*>(a->peer_base[r]);
+
+  const void* a_ptr = a->A;
+  uint64_t a_rows = a->M;
+  p.rpo = a->M;
+  p.own_lo_mb = 0;
+  p.own_hi_mb = p.MB - 1;
+  const bool dist = a->mode != KB_GEMM_PLAIN && a->world > 1;
+  if (a->mode == KB_GEMM_PLAIN || !dist) {
+    if (a->mode == KB_GEMM_AG) {
+      // Single rank: nothing to gather, read A in place.
+      p.mode = KB_GEMM_PLAIN;
+    }
+    if (a->mode == KB_GEMM_RS) p.mode = KB_GEMM_PLAIN;
+    p.world = 1;
+    p.rank = 0;
+  } else {
+    if (a->M % a->world != 0) {
+      kb::set_error("kb_gemm: M=%d must be divisible by world=%d", a->M, a->world);
+      return KB_ERR_ARG;
+    }
+    p.rpo = a->M / a->world;
+    if (!((p.rpo % BM) == 0 || (BM % p.rpo) == 0)) {
+      kb::set_error("kb_gemm: rows per rank (%d) must divide or be a multiple of %d", p.rpo, BM);
+      return KB_ERR_ARG;
+    }
+    for (int r = 0; r < a->world; ++r) {
+      if (p.peer_base[r] == nullptr) {
+        kb::set_error("kb_gemm: peer_base[%d] is null", r);
+        return KB_ERR_ARG;
+      }
+    }
+    p.own_lo_mb = (a->rank * p.rpo) / BM;
+    p.own_hi_mb = ((a->rank + 1) * p.rpo - 1) / BM;
+    if (a->mode == KB_GEMM_AG) {
+      p.a_local = static_cast<const bf16*>(a->A);
+      const uint32_t parity = a->epoch & 1u;
+      a_ptr = p.peer_base[a->rank] + a->data_off + (uint64_t)parity * a->M * a->K * 2;
+    }
+  }
+
+  int rc = make_tmap(&p.tmA, a_ptr, a_rows, a->K, BM);
+  if (rc != KB_OK) return rc;
+  rc = make_tmap(&p.tmB, a->B, a->N, a->K, BN);
+  if (rc != KB_OK) return rc;
+
+  int dev = 0, sms = 0;
+  KB_CUDA_OK(cudaGetDevice(&dev));
+  KB_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int total_tiles = p.MB * p.NB;
+  int grid = a->num_ctas > 0 ? a->num_ctas : sms;
+  if (grid > sms) grid = sms;
+  const bool ag = (p.mode == KB_GEMM_AG);
+  if (!ag && grid > total_tiles) grid = total_tiles;
+
+  static bool attr_done[2] = {false, false};
+  if (ag) {
+    if (!attr_done[1]) {
+      KB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      attr_done[1] = true;
+    }
+    gemm_kernel<true><<<grid, THREADS_AG, SMEM_BYTES, stream>>>(p);
+  } else {
+    if (!attr_done[0]) {
+      KB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      attr_done[0] = true;
+    }
+    gemm_kernel<false><<<grid, THREADS_BASE, SMEM_BYTES, stream>>>(p);
+  }
+  KB_CUDA_OK(cudaGetLastError());
+  return KB_OK;
+}

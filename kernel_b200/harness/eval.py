@@ -1,0 +1,525 @@
+"""Multi-process evaluator: correctness first, then device-timed benchmarks.
+
+Command line and protocol follow the reference's ``eval.py`` (``main``
+``:527-574``): ``POPCORN_FD=<fd> [POPCORN_SEED=<n>] [POPCORN_GPUS=<n>] python -m
+kernel_b200.harness.eval <mode> <tests-file>`` with modes ``test``,
+``benchmark``, ``leaderboard`` and ``profile``; ``key: value`` lines go to the
+inherited descriptor (``PopcornOutput`` ``:25-40``); exit codes 0 / 2 / 111 /
+112 / 113 keep their meaning.
+
+What differs from the reference, on purpose:
+
+* times are device times: a CUDA event pair around ``custom_kernel`` alone on
+  every rank, MAX over ranks (the reference times rank 0's wall clock around the
+  input clone too, ``eval.py:354-367``);
+* the any-rank-failed flag is an all-reduce, so no rank is left behind in a
+  broadcast when another rank fails (``eval.py:376-400``);
+* the rendezvous port is a free port unless ``MASTER_PORT`` is set, the
+  world size is validated against the pool size up front, ``leaderboard`` and
+  ``profile`` return a proper exit status, and ``profile`` works for
+  distributed tasks (per-rank table, rank 0 reported);
+* the task is a package (``--task all2all|gemm_rs|ag_gemm``; guessed from the
+  case keys otherwise), the implementation is selectable (``--impl
+  fused|baseline``) and the backend/device are parameters (``--backend
+  nccl|gloo``), so the same flow runs on CPU ranks;
+* a tests file may be replaced by ``--yaml <task.yml> --section tests|benchmarks``.
+"""
+from __future__ import annotations
+
+import argparse
+import base64
+import dataclasses
+import importlib
+import json
+import multiprocessing
+import os
+import socket
+import sys
+import time
+from pathlib import Path
+from typing import Any, List, Optional, Tuple
+
+import torch
+
+from ..utils.common import clear_l2_cache, set_seed
+from .stats import Stats, calculate_stats, should_stop
+from .testcases import SpecError, TestCase, cases_from_yaml, mix_seed, parse_tests
+
+EXIT_OK, EXIT_USAGE, EXIT_NO_FD, EXIT_FAIL, EXIT_BAD_TESTS = 0, 2, 111, 112, 113
+TEST_TIMEOUT_S, BENCH_TIMEOUT_S = 120, 240
+
+
+class PopcornOutput:
+    """``key: value`` line writer on an inherited file descriptor."""
+
+    def __init__(self, fd: int):
+        self.file = os.fdopen(fd, "w")
+        os.set_inheritable(fd, False)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.file.close()
+
+    def print(self, *args, **kwargs):
+        print(*args, **kwargs, file=self.file, flush=True)
+
+    def log(self, key: str, value: Any) -> None:
+        self.print(f"{key}: {value}")
+
+
+@dataclasses.dataclass
+class RunConfig:
+    task: str
+    impl: str
+    backend: str
+    port: int
+
+    def modules(self):
+        ref = importlib.import_module(f"kernel_b200.tasks.{self.task}.reference")
+        if self.impl == "fused":
+            sub = importlib.import_module(f"kernel_b200.tasks.{self.task}.submission")
+        elif self.impl == "baseline":
+            sub = importlib.import_module(f"kernel_b200.baseline.{self.task}")
+        else:
+            raise ValueError(f"unknown impl {self.impl!r}")
+        return ref, sub
+
+
+def guess_task(args: dict) -> str:
+    if "num_experts" in args:
+        return "all2all"
+    if args.get("op") == "ag_gemm":
+        return "ag_gemm"
+    return "gemm_rs"
+
+
+def free_port() -> int:
+    env = os.environ.get("MASTER_PORT")
+    if env:
+        return int(env)
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _device_for(rank: int, backend: str) -> torch.device:
+    if backend == "nccl":
+        return torch.device("cuda", rank)
+    return torch.device("cpu")
+
+
+def clone_data(data, device: torch.device):
+    """Deep copy of every tensor reachable through tuples, lists, dicts and plain
+    objects' attributes, placed on ``device`` (the reference's ``_clone_data``
+    stops at objects, ``eval.py:127-141``, and hands the originals to the kernel)."""
+    if isinstance(data, torch.Tensor):
+        return data.detach().clone().to(device)
+    if isinstance(data, tuple):
+        return tuple(clone_data(x, device) for x in data)
+    if isinstance(data, list):
+        return [clone_data(x, device) for x in data]
+    if isinstance(data, dict):
+        return {k: clone_data(v, device) for k, v in data.items()}
+    if dataclasses.is_dataclass(data) and not isinstance(data, type):
+        return data
+    if hasattr(data, "__dict__") and any(isinstance(v, torch.Tensor) for v in vars(data).values()):
+        twin = object.__new__(type(data))
+        for k, v in vars(data).items():
+            setattr(twin, k, clone_data(v, device))
+        return twin
+    return data
+
+
+def wrap_check(ref_mod, data, output) -> Tuple[bool, str]:
+    res = ref_mod.check_implementation(data, output)
+    if isinstance(res, tuple):
+        return bool(res[0]), str(res[1])
+    return (not bool(res)), str(res)
+
+
+def _case_args(test: TestCase, rank: Optional[int], device: torch.device) -> dict:
+    args = {k: v for k, v in test.args.items() if k != "op"}
+    if rank is not None:
+        args["rank"] = rank
+    args["device"] = device
+    return args
+
+
+def _sync(device: torch.device) -> None:
+    if device.type == "cuda":
+        torch.cuda.synchronize(device)
+
+
+class _Group:
+    """Process-group lifetime of one test, as in ``eval.py:167-184`` of the reference."""
+
+    def __init__(self, cfg: RunConfig, rank: int, world: int):
+        self.cfg, self.rank, self.world = cfg, rank, world
+        self.device = _device_for(rank, cfg.backend)
+        self.sub = None
+
+    def __enter__(self):
+        import torch.distributed as dist
+
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(self.cfg.port)
+        kwargs = {}
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+            kwargs["device_id"] = self.device
+        dist.init_process_group(self.cfg.backend, init_method="env://", rank=self.rank, world_size=self.world, **kwargs)
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        import torch.distributed as dist
+
+        try:
+            if self.sub is not None and hasattr(self.sub, "release_contexts") and exc_type is None:
+                self.sub.release_contexts()
+        finally:
+            dist.destroy_process_group()
+        return False
+
+
+def _any_failed(failed: bool, device: torch.device) -> bool:
+    import torch.distributed as dist
+
+    flag = torch.tensor([1 if failed else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    return bool(flag.item())
+
+
+# --------------------------------------------------------------------- test ----
+def run_distributed_test(cfg: RunConfig, test: TestCase, rank: int) -> Tuple[bool, str]:
+    world = test.args["world_size"]
+    with _Group(cfg, rank, world) as g:
+        ref, sub = cfg.modules()
+        g.sub = sub
+        data = ref.generate_input(**_case_args(test, rank, g.device))
+        _sync(g.device)
+        out = sub.custom_kernel(clone_data(data, g.device))
+        _sync(g.device)
+        return wrap_check(ref, data, out)
+
+
+def run_local_test(cfg: RunConfig, test: TestCase) -> Tuple[bool, str]:
+    device = torch.device("cuda", 0) if cfg.backend == "nccl" else torch.device("cpu")
+    ref, sub = cfg.modules()
+    args = _case_args(test, None, device)
+    args.setdefault("rank", 0)
+    args.setdefault("world_size", 1)
+    data = ref.generate_input(**args)
+    _sync(device)
+    out = sub.custom_kernel(clone_data(data, device))
+    _sync(device)
+    return wrap_check(ref, data, out)
+
+
+# ---------------------------------------------------------------- benchmark ----
+def _timed_call(fn, device: torch.device) -> Tuple[Any, float]:
+    """Runs ``fn`` once; returns (result, elapsed ns) measured on the device when
+    there is one (CUDA events on the launching stream)."""
+    if device.type == "cuda":
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out = fn()
+        end.record()
+        torch.cuda.synchronize(device)
+        return out, start.elapsed_time(end) * 1e6
+    t0 = time.perf_counter_ns()
+    out = fn()
+    return out, float(time.perf_counter_ns() - t0)
+
+
+def run_distributed_benchmark(cfg: RunConfig, test: TestCase, rank: int, recheck: bool, max_repeats: int,
+                              max_time_ns: float):
+    import torch.distributed as dist
+
+    world = test.args["world_size"]
+    with _Group(cfg, rank, world) as g:
+        ref, sub = cfg.modules()
+        g.sub = sub
+        dev = g.device
+        args = dict(test.args)
+        data = ref.generate_input(**_case_args(TestCase(args, test.spec), rank, dev))
+        out = sub.custom_kernel(clone_data(data, dev))
+        good, message = wrap_check(ref, data, out)
+        if _any_failed(not good, dev):
+            return message or "a peer rank failed the correctness check"
+        durations: List[float] = []
+        t_begin = time.perf_counter_ns()
+        for i in range(max_repeats):
+            if recheck:
+                if "seed" in args:
+                    args["seed"] += 13
+                data = ref.generate_input(**_case_args(TestCase(args, test.spec), rank, dev))
+            work = clone_data(data, dev)  # outside the timed region
+            clear_l2_cache(dev if dev.type == "cuda" else None)
+            _sync(dev)
+            dist.barrier()
+            out, ns = _timed_call(lambda: sub.custom_kernel(work), dev)
+            t = torch.tensor([ns], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            durations.append(float(t.item()))
+            message = None
+            if recheck:
+                good, msg = wrap_check(ref, data, out)
+                message = None if good else msg
+            del out
+            if _any_failed(message is not None, dev):
+                return message or "a peer rank failed the re-check"
+            stop = False
+            if rank == 0 and i > 1:
+                stop = should_stop(calculate_stats(durations), max_time_ns, time.perf_counter_ns() - t_begin)
+            flag = torch.tensor([1 if stop else 0], dtype=torch.int32, device=dev)
+            dist.broadcast(flag, 0)
+            if flag.item():
+                break
+        return calculate_stats(durations)
+
+
+def run_local_benchmark(cfg: RunConfig, test: TestCase, recheck: bool, max_repeats: int, max_time_ns: float):
+    dev = torch.device("cuda", 0) if cfg.backend == "nccl" else torch.device("cpu")
+    ref, sub = cfg.modules()
+    args = dict(test.args)
+    args.setdefault("rank", 0)
+    args.setdefault("world_size", 1)
+    data = ref.generate_input(**_case_args(TestCase(args, test.spec), None, dev))
+    out = sub.custom_kernel(clone_data(data, dev))
+    good, message = wrap_check(ref, data, out)
+    if not good:
+        return message
+    durations: List[float] = []
+    t_begin = time.perf_counter_ns()
+    for i in range(max_repeats):
+        if recheck:
+            if "seed" in args:
+                args["seed"] += 13
+            data = ref.generate_input(**_case_args(TestCase(args, test.spec), None, dev))
+        work = clone_data(data, dev)
+        clear_l2_cache(dev if dev.type == "cuda" else None)
+        _sync(dev)
+        out, ns = _timed_call(lambda: sub.custom_kernel(work), dev)
+        if recheck:
+            good, message = wrap_check(ref, data, out)
+            if not good:
+                return message
+        del out
+        durations.append(ns)
+        if i > 1 and should_stop(calculate_stats(durations), max_time_ns, time.perf_counter_ns() - t_begin):
+            break
+    return calculate_stats(durations)
+
+
+# ------------------------------------------------------------------ profile ----
+def run_profile(cfg: RunConfig, test: TestCase, rank: int) -> str:
+    from torch.profiler import ProfilerActivity, profile
+
+    world = test.args.get("world_size")
+
+    def body(device, rank_arg):
+        ref, sub = cfg.modules()
+        args = _case_args(test, rank_arg, device)
+        args.setdefault("rank", 0)
+        args.setdefault("world_size", 1)
+        data = ref.generate_input(**args)
+        work = clone_data(data, device)
+        sub.custom_kernel(work)  # warm-up: workspace creation is not the kernel
+        _sync(device)
+        acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if device.type == "cuda" else [])
+        with profile(activities=acts) as prof:
+            sub.custom_kernel(work)
+            _sync(device)
+        key = "self_cuda_time_total" if device.type == "cuda" else "self_cpu_time_total"
+        return sub, prof.key_averages().table(sort_by=key, row_limit=20)
+
+    if world is None:
+        return body(torch.device("cuda", 0) if cfg.backend == "nccl" else torch.device("cpu"), None)[1]
+    with _Group(cfg, rank, world) as g:
+        g.sub, table = body(g.device, rank)
+        return table
+
+
+# --------------------------------------------------------------- pool front ----
+class Runner:
+    """Dispatches the per-rank workers of every case onto a spawn pool."""
+
+    def __init__(self, pool, n_gpus: int, task: Optional[str], impl: str, backend: str):
+        self.pool, self.n_gpus, self.task, self.impl, self.backend = pool, n_gpus, task, impl, backend
+
+    def _cfg(self, test: TestCase) -> RunConfig:
+        return RunConfig(task=self.task or guess_task(test.args), impl=self.impl, backend=self.backend, port=free_port())
+
+    def _world(self, test: TestCase) -> Optional[int]:
+        world = test.args.get("world_size")
+        if world is not None and world > self.n_gpus:
+            raise SpecError(f"world_size {world} exceeds the {self.n_gpus} worker processes (POPCORN_GPUS)")
+        return world
+
+    def test(self, test: TestCase) -> Tuple[bool, str]:
+        try:
+            world = self._world(test)
+        except SpecError as e:
+            return False, str(e)
+        cfg = self._cfg(test)
+        if world is None:
+            return self.pool.apply(run_local_test, (cfg, test))
+        pending = [self.pool.apply_async(run_distributed_test, (cfg, test, r)) for r in range(world)]
+        results = []
+        for r, p in enumerate(pending):
+            try:
+                results.append(p.get(TEST_TIMEOUT_S))
+            except multiprocessing.TimeoutError:
+                results.append((False, f"timed out after {TEST_TIMEOUT_S} s"))
+            except Exception as e:  # worker raised
+                results.append((False, f"{type(e).__name__}: {e}"))
+        ok = all(r[0] for r in results)
+        errors = "\n".join(f"rank {i} - {r[1]}" for i, r in enumerate(results) if not r[0])
+        return ok, errors
+
+    def benchmark(self, test: TestCase, recheck: bool, max_repeats: int, max_time_ns: float):
+        try:
+            world = self._world(test)
+        except SpecError as e:
+            return str(e)
+        cfg = self._cfg(test)
+        if world is None:
+            return self.pool.apply(run_local_benchmark, (cfg, test, recheck, max_repeats, max_time_ns))
+        pending = [self.pool.apply_async(run_distributed_benchmark, (cfg, test, r, recheck, max_repeats, max_time_ns))
+                   for r in range(world)]
+        results = []
+        for p in pending:
+            try:
+                results.append(p.get(BENCH_TIMEOUT_S))
+            except multiprocessing.TimeoutError:
+                results.append(f"timed out after {BENCH_TIMEOUT_S} s")
+            except Exception as e:
+                results.append(f"{type(e).__name__}: {e}")
+        failed = [(i, r) for i, r in enumerate(results) if not isinstance(r, Stats)]
+        if failed:
+            return "\n".join(f"rank {i} - {msg}" for i, msg in failed)
+        return results[0]  # every rank holds the same MAX-reduced samples
+
+    def profile(self, test: TestCase) -> str:
+        world = self._world(test)
+        cfg = self._cfg(test)
+        if world is None:
+            return self.pool.apply(run_profile, (cfg, test, 0))
+        pending = [self.pool.apply_async(run_profile, (cfg, test, r)) for r in range(world)]
+        return [p.get(BENCH_TIMEOUT_S) for p in pending][0]
+
+
+def _log_stats(logger: PopcornOutput, idx: int, stats: Stats) -> None:
+    for field in dataclasses.fields(Stats):
+        logger.log(f"benchmark.{idx}.{field.name}", getattr(stats, field.name))
+    logger.log(f"benchmark.{idx}.max_rank_us", stats.mean / 1e3)
+
+
+def run_testing(logger: PopcornOutput, runner: Runner, tests: List[TestCase]) -> int:
+    passed = True
+    logger.log("test-count", len(tests))
+    for idx, test in enumerate(tests):
+        logger.log(f"test.{idx}.spec", test.spec)
+        good, message = runner.test(test)
+        if good:
+            logger.log(f"test.{idx}.status", "pass")
+            if message:
+                logger.log(f"test.{idx}.message", message)
+        else:
+            logger.log(f"test.{idx}.status", "fail")
+            logger.log(f"test.{idx}.error", message)
+            passed = False
+    logger.log("check", "pass" if passed else "fail")
+    return EXIT_OK if passed else EXIT_FAIL
+
+
+def run_benchmarking(logger: PopcornOutput, runner: Runner, tests: List[TestCase], leaderboard: bool) -> int:
+    runner.benchmark(tests[0], False, 100, 1e7 if leaderboard else 1e8)  # warm-up
+    logger.log("benchmark-count", len(tests))
+    passed = True
+    for idx, test in enumerate(tests):
+        logger.log(f"benchmark.{idx}.spec", test.spec)
+        result = runner.benchmark(test, leaderboard, 100, 30e9 if leaderboard else 10e9)
+        if isinstance(result, Stats):
+            _log_stats(logger, idx, result)
+        else:
+            passed = False
+            logger.log(f"benchmark.{idx}.status", "fail")
+            logger.log(f"benchmark.{idx}.error", str(result))
+            if leaderboard:
+                break
+    logger.log("check", "pass" if passed else "fail")
+    return EXIT_OK if passed else EXIT_FAIL
+
+
+def run_profiling(logger: PopcornOutput, runner: Runner, tests: List[TestCase]) -> int:
+    logger.log("benchmark-count", len(tests))
+    for idx, test in enumerate(tests):
+        logger.log(f"benchmark.{idx}.spec", test.spec)
+        report = runner.profile(test)
+        logger.log(f"benchmark.{idx}.report", base64.b64encode(report.encode("utf-8"), b"+*").decode("utf-8"))
+    logger.log("check", "pass")
+    return EXIT_OK
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    fd = os.getenv("POPCORN_FD")
+    if not fd:
+        return EXIT_NO_FD
+    ap = argparse.ArgumentParser(prog="kernel_b200.harness.eval", add_help=True)
+    ap.add_argument("mode", nargs="?")
+    ap.add_argument("tests_file", nargs="?")
+    ap.add_argument("--task", choices=["all2all", "gemm_rs", "ag_gemm"])
+    ap.add_argument("--impl", choices=["fused", "baseline"], default="fused")
+    ap.add_argument("--backend", choices=["nccl", "gloo"], default="nccl" if torch.cuda.is_available() else "gloo")
+    ap.add_argument("--yaml")
+    ap.add_argument("--section", default=None)
+    ap.add_argument("--world", type=int, default=None, help="override world_size of every case")
+    try:
+        ns = ap.parse_args(argv)
+    except SystemExit:
+        return EXIT_USAGE
+    if ns.mode is None or (ns.tests_file is None and ns.yaml is None):
+        return EXIT_USAGE
+    if ns.mode not in ("test", "benchmark", "leaderboard", "profile"):
+        return EXIT_USAGE
+
+    seed_env = os.getenv("POPCORN_SEED")
+    os.environ.pop("POPCORN_SEED", None)
+    seed = int(seed_env) if seed_env else None
+    n_gpus = int(os.getenv("POPCORN_GPUS", "1"))
+    set_seed(seed or 42)
+    try:
+        if ns.yaml:
+            section = ns.section or ("tests" if ns.mode == "test" else "benchmarks")
+            tests = cases_from_yaml(ns.yaml, section, seed)
+        else:
+            tests = parse_tests(Path(ns.tests_file).read_text(), seed)
+    except (OSError, SpecError) as e:
+        print(f"Could not read test cases: {e}", file=sys.stderr)
+        return EXIT_BAD_TESTS
+    if not tests:
+        print("no test cases", file=sys.stderr)
+        return EXIT_BAD_TESTS
+    if ns.world is not None:
+        for t in tests:
+            if "world_size" in t.args:
+                t.args["world_size"] = ns.world
+
+    with PopcornOutput(int(fd)) as logger:
+        ctx = multiprocessing.get_context("spawn")
+        with ctx.Pool(n_gpus) as pool:
+            runner = Runner(pool, n_gpus, ns.task, ns.impl, ns.backend)
+            if ns.mode == "test":
+                return run_testing(logger, runner, tests)
+            if ns.mode == "benchmark":
+                return run_benchmarking(logger, runner, tests, leaderboard=False)
+            if ns.mode == "leaderboard":
+                return run_benchmarking(logger, runner, tests, leaderboard=True)
+            return run_profiling(logger, runner, tests)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

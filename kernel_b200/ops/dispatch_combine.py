@@ -1,0 +1,223 @@
+"""MoE expert-parallel dispatch / combine.
+
+``MoEAllToAll`` owns the symmetric workspace of one configuration and exposes
+``dispatch`` -> (expert compute) -> ``combine`` plus the fused
+``dispatch_scale_combine`` round trip the all2all task measures.  On CUDA it
+launches the hand-written kernels in ``csrc/kernels/a2a.cu`` (no NCCL call, no
+host synchronisation, no allocation after construction apart from the output
+tensor).  On CPU it runs a vectorised torch implementation over
+``torch.distributed`` so that the routing logic can be tested with gloo.
+
+Reference counterparts: ``reference.py:54-234`` (``PyTorchAllToAll``) and
+``submission.py:5-219`` (``OptimizedAllToAll`` / ``custom_kernel``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import _native as N
+from ..parallel.symm import SymmHeap, _dist_info
+
+_WAIT_LIMIT_NS = int(float(os.environ.get("KB200_WAIT_LIMIT_MS", "2000")) * 1e6)
+_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+SCALE_IDENTITY, SCALE_RANK, SCALE_EXPERT = 0, 1, 2
+
+launch_count = 0  # kernels launched by this module (bench accounting)
+
+
+def expert_scale_vector(num_experts: int, world: int, mode: int, device=None) -> torch.Tensor:
+    """Per-expert multiplier of the simulated expert, as a float32 vector [E]."""
+    e = torch.arange(num_experts, device=device)
+    if mode == SCALE_IDENTITY:
+        return torch.ones(num_experts, device=device)
+    if mode == SCALE_RANK:
+        return (1 + e // (num_experts // world)).float()
+    if mode == SCALE_EXPERT:
+        return (e + 1).float() / num_experts
+    raise ValueError(f"unknown scale mode {mode}")
+
+
+class MoEAllToAll:
+    def __init__(self, num_experts: int, experts_per_token: int, hidden_dim: int, max_num_tokens: int,
+                 dtype: torch.dtype = torch.bfloat16, group=None, device: Optional[torch.device] = None,
+                 heap: Optional[SymmHeap] = None):
+        self.E, self.k, self.H, self.max_tokens = num_experts, experts_per_token, hidden_dim, max_num_tokens
+        self.dtype = dtype
+        self.group = group
+        self.rank, self.world = _dist_info(group)
+        if num_experts % self.world:
+            raise ValueError("num_experts must be divisible by the world size")
+        self.El = num_experts // self.world
+        self.cap = max_num_tokens * experts_per_token
+        self.native = torch.cuda.is_available() and (device is None or torch.device(device).type == "cuda")
+        self.epoch = 0
+        self.heap = None
+        if self.native:
+            if dtype not in _DTYPES:
+                raise ValueError(f"unsupported dtype {dtype}")
+            lib = N.lib()
+            eb = torch.empty((), dtype=dtype).element_size()
+            rows = int(lib.kb_a2a_rows_bytes(self.world, max_num_tokens, experts_per_token, hidden_dim, eb))
+            counts = (self.world * self.El * 4 + 255) // 256 * 256
+            need = 2 * rows + counts + 256 + 256 + 4096
+            self.heap = heap or SymmHeap(need, group=group, device=device)
+            self.recv_off = self.heap.alloc(rows)
+            self.y_off = self.heap.alloc(rows)
+            self.count_off = self.heap.alloc(counts)
+            self.flag_off = self.heap.alloc(256)
+            self.sync_off = self.heap.alloc(256)
+            self.slots = torch.empty(self.cap, dtype=torch.int32, device=self.heap.device)
+            self.status = self.heap.status
+            self._eb = eb
+
+    # ------------------------------------------------------------- native ----
+    def _args(self, x, indices, weights, out, scale_mode) -> N.A2aArgs:
+        a = N.A2aArgs()
+        a.rank, a.world = self.rank, self.world
+        a.num_experts, a.topk, a.hidden, a.max_tokens = self.E, self.k, self.H, self.max_tokens
+        a.num_tokens = x.shape[0]
+        a.elem_bytes, a.dtype = self._eb, _DTYPES[self.dtype]
+        a.x, a.indices = x.data_ptr(), indices.data_ptr()
+        a.weights = weights.data_ptr() if weights is not None else None
+        a.out = out.data_ptr() if out is not None else None
+        a.slots = self.slots.data_ptr()
+        a.epoch = self.epoch
+        a.peer_base = self.heap.peer_array()
+        a.recv_off, a.y_off, a.count_off = self.recv_off, self.y_off, self.count_off
+        a.flag_off, a.sync_off = self.flag_off, self.sync_off
+        a.scale_mode = scale_mode
+        a.status = self.status.data_ptr()
+        a.wait_limit_ns = _WAIT_LIMIT_NS
+        return a
+
+    def _validate(self, x, indices, weights) -> None:
+        T = x.shape[0]
+        if x.dtype != self.dtype or x.shape[1] != self.H or not x.is_contiguous():
+            raise ValueError("x must be contiguous [T, hidden] in the context dtype")
+        if indices.dtype != torch.int32 or tuple(indices.shape) != (T, self.k) or not indices.is_contiguous():
+            raise ValueError("indices must be contiguous int32 [T, k]")
+        if weights is not None and (weights.dtype != torch.float32 or tuple(weights.shape) != (T, self.k) or not weights.is_contiguous()):
+            raise ValueError("weights must be contiguous float32 [T, k]")
+        if T > self.max_tokens:
+            raise ValueError("more tokens than max_num_tokens")
+
+    def dispatch_scale_combine(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
+                               scale_mode: int = SCALE_IDENTITY) -> torch.Tensor:
+        """Full round trip with the simulated expert ``y = scale(expert) * x``."""
+        self._validate(x, indices, weights)
+        if not x.is_cuda:
+            return self._cpu_round_trip(x, indices, weights, scale_mode)
+        global launch_count
+        out = torch.empty_like(x)
+        self.epoch += 1
+        a = self._args(x, indices, weights, out, scale_mode)
+        lib = N.lib()
+        st = torch.cuda.current_stream(x.device).cuda_stream
+        N.check(lib.kb_a2a_dispatch(C.byref(a), st))
+        N.check(lib.kb_a2a_expert_scale(C.byref(a), st))
+        N.check(lib.kb_a2a_combine(C.byref(a), st))
+        launch_count += 3
+        return out
+
+    def dispatch(self, x: torch.Tensor, indices: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Pushes token rows to their experts' ranks.
+
+        Returns ``(counts, recv)``: ``counts[src, local_expert]`` (int32) and the
+        receive region ``recv[src, row, H]`` of this rank; the rows of one
+        source are grouped by local expert in expert order.  Both alias the
+        symmetric workspace and are valid once the stream has passed the wait
+        that ``expert_rows`` / ``combine`` enqueue.
+        """
+        self._validate(x, indices, None)
+        if not x.is_cuda:
+            raise RuntimeError("split dispatch/combine needs the CUDA path; use dispatch_scale_combine on CPU")
+        global launch_count
+        self.epoch += 1
+        a = self._args(x, indices, None, None, SCALE_IDENTITY)
+        lib = N.lib()
+        st = torch.cuda.current_stream(x.device).cuda_stream
+        N.check(lib.kb_a2a_dispatch(C.byref(a), st))
+        flags = self.heap.peer_ptr(self.rank) + self.flag_off
+        N.check(lib.kb_wait_flags(flags, self.world, self.epoch, _WAIT_LIMIT_NS, self.status.data_ptr(), st))
+        launch_count += 2
+        counts = self.heap.tensor(self.count_off, (self.world, self.El), torch.int32)
+        recv = self.heap.tensor(self.recv_off, (self.world, self.cap, self.H), self.dtype)
+        return counts, recv
+
+    def expert_output_buffer(self) -> torch.Tensor:
+        """``y[src, row, H]``: where expert outputs must be written, row for row."""
+        return self.heap.tensor(self.y_off, (self.world, self.cap, self.H), self.dtype)
+
+    def combine(self, x_like: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """Publishes this rank's expert outputs and gathers the weighted sum
+        ``out[t] = sum_k w[t,k] * y(t,k)`` for the local tokens."""
+        self._validate(x_like, indices, weights)
+        global launch_count
+        out = torch.empty_like(x_like)
+        a = self._args(x_like, indices, weights, out, SCALE_IDENTITY)
+        lib = N.lib()
+        st = torch.cuda.current_stream(x_like.device).cuda_stream
+        # y-ready flags of this epoch go out through a barrier-style post.
+        pad = self.flag_off + 4 * self.world
+        N.check(lib.kb_device_barrier(self.heap.peer_array(), pad, self.rank, self.world, self.epoch, _WAIT_LIMIT_NS,
+                                      self.status.data_ptr(), st))
+        N.check(lib.kb_a2a_combine(C.byref(a), st))
+        launch_count += 2
+        return out
+
+    def expert_view(self, counts: torch.Tensor, recv: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Expert-major padded view ``(expert_num_tokens [El], expert_x [El, max_recv, H])``
+        like ``PyTorchAllToAll.dispatch`` returns (reference.py:123-148).  Copies."""
+        counts_h = counts.cpu()
+        max_recv = self.max_tokens * self.world
+        ex = torch.zeros((self.El, max_recv, self.H), dtype=self.dtype, device=recv.device)
+        num = counts_h.sum(0).to(torch.int32)
+        fill = [0] * self.El
+        for s in range(self.world):
+            off = 0
+            for le in range(self.El):
+                c = int(counts_h[s, le])
+                if c:
+                    ex[le, fill[le]:fill[le] + c] = recv[s, off:off + c]
+                    fill[le] += c
+                off += c
+        return num.to(recv.device), ex
+
+    # ---------------------------------------------------------------- CPU ----
+    def _cpu_round_trip(self, x, indices, weights, scale_mode) -> torch.Tensor:
+        T = x.shape[0]
+        flat_e = indices.reshape(-1).long()
+        dst = flat_e // self.El
+        order = torch.argsort(dst, stable=True)
+        send_counts = torch.bincount(dst, minlength=self.world)
+        tok = torch.arange(T).repeat_interleave(self.k)
+        send_x = x[tok][order]
+        send_e = flat_e[order]
+        if self.world > 1:
+            recv_counts = torch.empty_like(send_counts)
+            dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+            rc, sc = recv_counts.tolist(), send_counts.tolist()
+            recv_x = torch.empty((sum(rc), self.H), dtype=x.dtype)
+            recv_e = torch.empty(sum(rc), dtype=torch.long)
+            dist.all_to_all_single(recv_x, send_x, rc, sc, group=self.group)
+            dist.all_to_all_single(recv_e, send_e, rc, sc, group=self.group)
+        else:
+            rc = sc = send_counts.tolist()
+            recv_x, recv_e = send_x, send_e
+        scale = expert_scale_vector(self.E, self.world, scale_mode)[recv_e].unsqueeze(1)
+        y = (recv_x.float() * scale).to(x.dtype)
+        if self.world > 1:
+            back = torch.empty_like(send_x)
+            dist.all_to_all_single(back, y, sc, rc, group=self.group)
+        else:
+            back = y
+        contrib = torch.empty_like(back)
+        contrib[order] = back
+        w = weights.reshape(-1, 1)
+        out = (contrib.float() * w).view(T, self.k, self.H).sum(1)
+        return out.to(x.dtype)

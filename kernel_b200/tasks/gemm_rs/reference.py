@@ -1,0 +1,106 @@
+"""Oracle of the GEMM + reduce-scatter task.
+
+Contract of the reference's ``gemm_rs/reference.py`` (``generate_input`` ``:5-33``,
+``ref_kernel`` ``:36-60``, ``check_implementation`` ``:63-71``) with the device as a
+parameter and two input distributions:
+
+* ``uniform``: input, weight and bias uniform in +-0.01 (the reference's draw);
+* ``normal``:  input ~ N(0,1), weight ~ N(0,1)/sqrt(K), bias ~ N(0,0.02).
+
+K is sharded: rank r holds ``input[M, K/world]`` and ``weight[N, K/world]``; the
+result ``sum_r input_r @ weight_r^T`` is row-scattered, rank r keeps rows
+``[r*M/world, (r+1)*M/world)``.  See ``task.py`` for the bias convention.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import task
+from .task import input_t, output_t
+
+RTOL, ATOL = 1e-2, 1e-2  # gemm_rs/reference.py:67
+
+
+def default_device(rank: int) -> torch.device:
+    if torch.cuda.is_available():
+        return torch.device("cuda", rank % torch.cuda.device_count())
+    return torch.device("cpu")
+
+
+def _world() -> int:
+    return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+
+
+def generate_input(rank: int, world_size: int, m: int, n: int, k: int, has_bias: bool, seed: int,
+                   dist: str = "uniform", bias_mode: Optional[str] = None, device=None) -> input_t:
+    dev = torch.device(device) if device is not None else default_device(rank)
+    if m % world_size or k % world_size:
+        raise ValueError("m and k must be divisible by world_size")
+    if bias_mode is not None:
+        task.set_bias_mode(bias_mode)
+    local_k = k // world_size
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed + rank)
+    if dist == "uniform":
+        a = ((torch.rand((m, local_k), device=dev, generator=gen) * 2 - 1) * 0.01).to(torch.bfloat16)
+        w = ((torch.rand((n, local_k), device=dev, generator=gen) * 2 - 1) * 0.01).to(torch.bfloat16)
+    elif dist == "normal":
+        a = torch.randn((m, local_k), device=dev, generator=gen).to(torch.bfloat16)
+        w = (torch.randn((n, local_k), device=dev, generator=gen) / k ** 0.5).to(torch.bfloat16)
+    else:
+        raise ValueError(f"unknown dist {dist!r}")
+    bias = None
+    if has_bias:
+        gen.manual_seed(seed)  # identical on every rank
+        if dist == "uniform":
+            bias = ((torch.rand((n,), device=dev, generator=gen) * 2 - 1) * 0.01).to(torch.bfloat16)
+        else:
+            bias = (torch.randn((n,), device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+    return a, w, bias
+
+
+def ref_kernel(data: input_t) -> output_t:
+    """``matmul`` -> bias -> ``reduce_scatter_tensor``, i.e. the library path."""
+    a, w, bias = data
+    world = _world()
+    M, N = a.shape[0], w.shape[0]
+    if a.is_cuda:
+        out = torch.matmul(a, w.t())
+    else:
+        out = (a.float() @ w.float().t()).to(torch.bfloat16)
+    per_rank = task.get_bias_mode() == "per_rank"
+    if bias is not None and per_rank:
+        out = out + bias
+    if world > 1:
+        rs = torch.empty((M // world, N), dtype=out.dtype, device=a.device)
+        dist.reduce_scatter_tensor(rs, out.contiguous())
+    else:
+        rs = out
+    if bias is not None and not per_rank:
+        rs = (rs.float() + bias.float()).to(rs.dtype)
+    return rs
+
+
+def ref_fp32(all_inputs, all_weights, bias, rank: int, bias_mode: str = "once") -> torch.Tensor:
+    """Collective-free fp32 oracle from every rank's shards (tests only)."""
+    world = len(all_inputs)
+    acc = sum(a.float() @ w.float().t() for a, w in zip(all_inputs, all_weights))
+    if bias is not None:
+        acc = acc + (world if bias_mode == "per_rank" else 1) * bias.float()
+    rows = acc.shape[0] // world
+    return acc[rank * rows:(rank + 1) * rows]
+
+
+def check_implementation(data: input_t, output: output_t):
+    expected = ref_kernel(data)
+    if output.device != expected.device:
+        return False, f"Output device mismatch: {output.device} != {expected.device}"
+    if output.shape != expected.shape:
+        return False, f"Output shape mismatch: {tuple(output.shape)} != {tuple(expected.shape)}"
+    if not torch.allclose(output.float(), expected.float(), rtol=RTOL, atol=ATOL):
+        diff = (output.float() - expected.float()).abs()
+        return False, f"Output values mismatch: max abs diff {diff.max().item():.5g}"
+    return True, ""

@@ -1,0 +1,42 @@
+"""``custom_kernel`` of the GEMM + reduce-scatter task: one fused sm_100a kernel.
+
+Counterpart of the reference's ``gemm_rs/submission.py:5-29`` (``torch.matmul``,
+bias add, ``reduce_scatter_tensor``).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ...ops.gemm import GemmRS
+from . import task
+from .task import input_t, output_t
+
+_contexts: dict = {}
+
+
+def _group_key():
+    return id(dist.group.WORLD) if dist.is_available() and dist.is_initialized() else None
+
+
+def get_context(M: int, N: int, device: torch.device) -> GemmRS:
+    key = (M, N, str(device), _group_key())
+    ctx = _contexts.get(key)
+    if ctx is None:
+        ctx = GemmRS(M, N, device=device)
+        _contexts[key] = ctx
+    return ctx
+
+
+def release_contexts() -> None:
+    for ctx in _contexts.values():
+        if ctx.heap is not None:
+            ctx.heap.close()
+    _contexts.clear()
+
+
+def custom_kernel(data: input_t) -> output_t:
+    a, w, bias = data
+    ctx = get_context(a.shape[0], w.shape[0], a.device)
+    scale = float(ctx.world) if task.get_bias_mode() == "per_rank" else 1.0
+    return ctx(a, w, bias, bias_scale=scale)
