@@ -120,6 +120,7 @@ def _declare(lib: C.CDLL) -> None:
         "kb_a2a_dispatch": (i, [C.POINTER(A2aArgs), vp]),
         "kb_a2a_expert_scale": (i, [C.POINTER(A2aArgs), vp]),
         "kb_a2a_combine": (i, [C.POINTER(A2aArgs), vp]),
+        "kb_a2a_round_trip": (i, [C.POINTER(A2aArgs), vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -145,6 +145,8 @@ uint64_t kb_a2a_rows_bytes(int world, int max_tokens, int topk, int hidden, int 
 int kb_a2a_dispatch(const KbA2aArgs* a, void* stream);
 int kb_a2a_expert_scale(const KbA2aArgs* a, void* stream);
 int kb_a2a_combine(const KbA2aArgs* a, void* stream);
+// dispatch + simulated expert + combine in ONE cooperative launch.
+int kb_a2a_round_trip(const KbA2aArgs* a, void* stream);
 
 #ifdef __cplusplus
 }

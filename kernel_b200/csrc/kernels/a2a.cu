@@ -32,7 +32,7 @@ namespace {
 
 constexpr int A2A_THREADS = 256;
 constexpr int MAX_EXPERTS = 1024;
-constexpr int MAX_ENT_PER_CTA = 512;
+constexpr int MAX_ENT_PER_CTA = 2048;
 
 enum Site : uint32_t { SITE_DISP_IDX = 11, SITE_EXP_FLAG = 12, SITE_COMB_FLAG = 13, SITE_COMB_SLOT = 14 };
 
@@ -83,8 +83,23 @@ __device__ __forceinline__ bool last_block_done(uint32_t* counter, uint32_t tota
 }
 
 // ------------------------------------------------------------------ dispatch ----
-__global__ void __launch_bounds__(A2A_THREADS) a2a_dispatch_kernel(const A2aParams p) {
-  extern __shared__ int32_t sh[];
+// Work unit u = (token group tg, hidden split hs); one unit per CTA.
+__device__ __forceinline__ void unit_ranges(const A2aParams& p, int& t0, int& t1, int& v0, int& v1, int& hs) {
+  const int tg = blockIdx.x / p.h_splits;
+  hs = blockIdx.x - tg * p.h_splits;
+  const int tok_per = (p.T + p.tok_groups - 1) / p.tok_groups;
+  t0 = min(tg * tok_per, p.T);
+  t1 = min(t0 + tok_per, p.T);
+  const int v_per = (p.vecs + p.h_splits - 1) / p.h_splits;
+  v0 = min(hs * v_per, p.vecs);
+  v1 = min(v0 + v_per, p.vecs);
+  if (blockIdx.x >= p.tok_groups * p.h_splits) {  // surplus CTAs of a fused launch
+    t0 = t1 = p.T;
+    v0 = v1 = 0;
+  }
+}
+
+__device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh) {
   int32_t* tot = sh;               // [E] entries per expert, whole rank
   int32_t* pre = tot + p.E;        // [E] entries per expert before this CTA's tokens
   int32_t* off = pre + p.E;        // [E] first slot of the expert inside its owner's region
@@ -92,10 +107,8 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_dispatch_kernel(const A2aPara
   int32_t* ent_slot = ent_e + MAX_ENT_PER_CTA;
 
   const int tid = threadIdx.x;
-  const int tg = blockIdx.x, hs = blockIdx.y;
-  const int tok_per = (p.T + p.tok_groups - 1) / p.tok_groups;
-  const int t0 = min(tg * tok_per, p.T);
-  const int t1 = min(t0 + tok_per, p.T);
+  int t0, t1, v0, v1, hs;
+  unit_ranges(p, t0, t1, v0, v1, hs);
   const int n_ent = (t1 - t0) * p.k;
   const int total_ent = p.T * p.k;
 
@@ -143,9 +156,6 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_dispatch_kernel(const A2aPara
   __syncthreads();
 
   // Payload: one 16-byte vector per thread, read once, stored k times.
-  const int v_per = (p.vecs + p.h_splits - 1) / p.h_splits;
-  const int v0 = min(hs * v_per, p.vecs);
-  const int v1 = min(v0 + v_per, p.vecs);
   for (int t = t0; t < t1; ++t) {
     const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(t) * p.row_bytes);
     for (int v = v0 + tid; v < v1; v += blockDim.x) {
@@ -161,15 +171,20 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_dispatch_kernel(const A2aPara
     }
   }
   // Per-(source, expert) counts for every destination.
-  if (tg == 0 && hs == 0) {
+  if (blockIdx.x == 0) {
     for (int e = tid; e < p.E; e += blockDim.x) {
       counts_ptr(p, e / p.El, p.rank)[e % p.El] = tot[e];
     }
   }
   uint32_t* sync = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.sync_off);
-  if (last_block_done(&sync[0], gridDim.x * gridDim.y)) {
+  if (last_block_done(&sync[0], gridDim.x)) {
     if (tid < p.world) kb::st_release_sys_u32(flag_ptr(p, tid, 0, p.rank), p.epoch);
   }
+}
+
+__global__ void __launch_bounds__(A2A_THREADS) a2a_dispatch_kernel(const A2aParams p) {
+  extern __shared__ int32_t sh[];
+  dispatch_body(p, sh);
 }
 
 // -------------------------------------------------------------- expert scale ----
@@ -229,9 +244,8 @@ struct Vec16<float> {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(A2A_THREADS) a2a_expert_kernel(const A2aParams p) {
-  extern __shared__ int32_t sh[];
-  int32_t* incl = sh;                     // [world][El] inclusive prefix of counts per source
+__device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh) {
+  int32_t* incl = sh;                        // [world][El] inclusive prefix of counts per source
   int32_t* src_end = incl + p.world * p.El;  // [world] inclusive prefix of per-source totals
   const int tid = threadIdx.x;
 
@@ -241,15 +255,20 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_expert_kernel(const A2aParams
     }
   }
   __syncthreads();
-  for (int s = tid; s < p.world; s += blockDim.x) {
-    const int32_t* c = counts_ptr(p, p.rank, s);
+  // All counts are fetched in parallel (one independent load per thread), then
+  // scanned in shared memory.
+  const int32_t* counts = counts_ptr(p, p.rank, 0);
+  for (int i = tid; i < p.world * p.El; i += blockDim.x) {
+    int v = static_cast<int>(kb::ld_relaxed_sys_u32(reinterpret_cast<const uint32_t*>(counts + i)));
+    incl[i] = v < 0 ? 0 : v;
+  }
+  __syncthreads();
+  if (tid < p.world) {
     int acc = 0;
     for (int le = 0; le < p.El; ++le) {
-      int v = static_cast<int>(kb::ld_relaxed_sys_u32(reinterpret_cast<const uint32_t*>(c + le)));
-      if (v < 0) v = 0;
-      acc += v;
+      acc += incl[tid * p.El + le];
       if (acc > p.cap) acc = p.cap;
-      incl[s * p.El + le] = acc;
+      incl[tid * p.El + le] = acc;
     }
   }
   __syncthreads();
@@ -292,9 +311,15 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_expert_kernel(const A2aParams
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(A2A_THREADS) a2a_expert_kernel(const A2aParams p) {
+  extern __shared__ int32_t sh[];
+  expert_body<T>(p, sh);
+}
+
 // ------------------------------------------------------------------- combine ----
 template <typename T>
-__global__ void __launch_bounds__(A2A_THREADS) a2a_combine_kernel(const A2aParams p) {
+__device__ __forceinline__ void combine_body(const A2aParams& p) {
   const int tid = threadIdx.x;
   if (tid < p.world) {
     if (!kb::wait_flag_ge(flag_ptr(p, p.rank, 1, tid), p.epoch, p.limit_ns)) {
@@ -302,41 +327,60 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_combine_kernel(const A2aParam
     }
   }
   __syncthreads();
-  const long long total = static_cast<long long>(p.T) * p.vecs;
-  for (long long g = static_cast<long long>(blockIdx.x) * blockDim.x + tid; g < total;
-       g += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int t = static_cast<int>(g / p.vecs);
-    const int v = static_cast<int>(g - static_cast<long long>(t) * p.vecs);
-    float acc[Vec16<T>::N];
+  int t0, t1, v0, v1, hs;
+  unit_ranges(p, t0, t1, v0, v1, hs);
+  for (int t = t0; t < t1; ++t) {
+    for (int v = v0 + tid; v < v1; v += blockDim.x) {
+      float acc[Vec16<T>::N];
 #pragma unroll
-    for (int i = 0; i < Vec16<T>::N; ++i) acc[i] = 0.f;
-    for (int k0 = 0; k0 < p.k; k0 += 8) {
-      uint4 u[8];
-      float wk[8];
+      for (int i = 0; i < Vec16<T>::N; ++i) acc[i] = 0.f;
+      for (int k0 = 0; k0 < p.k; k0 += 8) {
+        uint4 u[8];
+        float wk[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int kk = k0 + j;
-        wk[j] = 0.f;
-        u[j] = make_uint4(0, 0, 0, 0);
-        if (kk < p.k) {
-          const int e = p.idx[t * p.k + kk];
-          const int slot = p.slots[t * p.k + kk];
-          if (e >= 0 && e < p.E && slot >= 0 && slot < p.cap) {
-            wk[j] = p.w[t * p.k + kk];
-            u[j] = kb::ld_sys_v4(reinterpret_cast<const uint4*>(rows_ptr(p, e / p.El, p.y_off, p.rank, slot)) + v);
+        for (int j = 0; j < 8; ++j) {
+          const int kk = k0 + j;
+          wk[j] = 0.f;
+          u[j] = make_uint4(0, 0, 0, 0);
+          if (kk < p.k) {
+            const int e = p.idx[t * p.k + kk];
+            const int slot = p.slots[t * p.k + kk];
+            if (e >= 0 && e < p.E && slot >= 0 && slot < p.cap) {
+              wk[j] = p.w[t * p.k + kk];
+              u[j] = kb::ld_sys_v4(reinterpret_cast<const uint4*>(rows_ptr(p, e / p.El, p.y_off, p.rank, slot)) + v);
+            }
           }
         }
-      }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float f[Vec16<T>::N];
-        Vec16<T>::load(u[j], f);
+        for (int j = 0; j < 8; ++j) {
+          float f[Vec16<T>::N];
+          Vec16<T>::load(u[j], f);
 #pragma unroll
-        for (int i = 0; i < Vec16<T>::N; ++i) acc[i] = fmaf(wk[j], f[i], acc[i]);
+          for (int i = 0; i < Vec16<T>::N; ++i) acc[i] = fmaf(wk[j], f[i], acc[i]);
+        }
       }
+      reinterpret_cast<uint4*>(p.out + static_cast<size_t>(t) * p.row_bytes)[v] = Vec16<T>::store(acc);
     }
-    reinterpret_cast<uint4*>(p.out + static_cast<size_t>(t) * p.row_bytes)[v] = Vec16<T>::store(acc);
   }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(A2A_THREADS) a2a_combine_kernel(const A2aParams p) {
+  combine_body<T>(p);
+}
+
+// All three phases in one cooperative launch: the phases are separated only by
+// the epoch flags (this rank's own flag doubles as the grid-wide barrier), so
+// the two extra launches and their gaps disappear.  Needs every CTA resident,
+// which the cooperative launch guarantees.
+template <typename T>
+__global__ void __launch_bounds__(A2A_THREADS) a2a_fused_kernel(const A2aParams p) {
+  extern __shared__ int32_t sh[];
+  dispatch_body(p, sh);
+  __syncthreads();
+  expert_body<T>(p, sh);
+  __syncthreads();
+  combine_body<T>(p);
 }
 
 // --------------------------------------------------------------- small utils ----
@@ -417,32 +461,37 @@ int fill_params(const KbA2aArgs* a, A2aParams* p, int sms) {
   p->scale_mode = a->scale_mode;
   p->status = a->status;
   p->limit_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
-  // Work split: enough CTAs to fill the machine about twice, token ranges
-  // small enough for the in-CTA ranking, hidden split so that a thread owns
-  // one vector of a row.
+  // Work split: one unit per CTA, about two CTAs per SM.  Units are token
+  // groups; with few tokens every group is further split along the hidden
+  // dimension so that more SMs take part.
   const int target = 2 * sms;
-  int hs = (p->vecs + A2A_THREADS - 1) / A2A_THREADS;
-  if (hs < 1) hs = 1;
-  int tg = (target + hs - 1) / hs;
   const int T = p->T > 0 ? p->T : 1;
-  if (tg > T) tg = T;
+  int tg = T < target ? T : target;
   const int min_tg = (T * p->k + MAX_ENT_PER_CTA - 1) / MAX_ENT_PER_CTA;
   if (tg < min_tg) tg = min_tg;
   if (tg > T) {
     kb::set_error("a2a: topk=%d too large for the per-CTA ranking buffer", p->k);
     return KB_ERR_ARG;
   }
-  // Few tokens: split rows finer so that more SMs take part.
-  while (tg * hs < sms && hs * 2 * 32 <= p->vecs) hs *= 2;
+  int hs = target / tg;
+  if (hs < 1) hs = 1;
+  const int max_hs = (p->vecs + 31) / 32;  // at least a warp's worth of vectors per unit
+  if (hs > max_hs) hs = max_hs;
   p->tok_groups = tg;
   p->h_splits = hs;
   return KB_OK;
 }
 
 int device_sms(int* sms) {
+  static int cached[64] = {0};
   int dev = 0;
   KB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) {
+    *sms = cached[dev];
+    return KB_OK;
+  }
   KB_CUDA_OK(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev));
+  if (dev >= 0 && dev < 64) cached[dev] = *sms;
   return KB_OK;
 }
 
@@ -461,8 +510,7 @@ extern "C" int kb_a2a_dispatch(const KbA2aArgs* a, void* stream) {
   rc = fill_params(a, &p, sms);
   if (rc != KB_OK) return rc;
   const size_t smem = (3 * p.E + 2 * MAX_ENT_PER_CTA) * sizeof(int32_t);
-  dim3 grid(p.tok_groups, p.h_splits);
-  a2a_dispatch_kernel<<<grid, A2A_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p);
+  a2a_dispatch_kernel<<<p.tok_groups * p.h_splits, A2A_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p);
   KB_CUDA_OK(cudaGetLastError());
   return KB_OK;
 }
@@ -494,20 +542,52 @@ extern "C" int kb_a2a_combine(const KbA2aArgs* a, void* stream) {
   A2aParams p;
   rc = fill_params(a, &p, sms);
   if (rc != KB_OK) return rc;
-  const long long total = static_cast<long long>(p.T) * p.vecs;
-  long long want = (total + A2A_THREADS - 1) / A2A_THREADS;
-  const long long cap = a->num_ctas > 0 ? a->num_ctas : 8LL * sms;
-  if (want > cap) want = cap;
-  if (want < 1) want = 1;
+  const int want = p.tok_groups * p.h_splits;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (a->dtype) {
-    case 0: a2a_combine_kernel<__nv_bfloat16><<<(int)want, A2A_THREADS, 0, st>>>(p); break;
-    case 1: a2a_combine_kernel<__half><<<(int)want, A2A_THREADS, 0, st>>>(p); break;
-    case 2: a2a_combine_kernel<float><<<(int)want, A2A_THREADS, 0, st>>>(p); break;
+    case 0: a2a_combine_kernel<__nv_bfloat16><<<want, A2A_THREADS, 0, st>>>(p); break;
+    case 1: a2a_combine_kernel<__half><<<want, A2A_THREADS, 0, st>>>(p); break;
+    case 2: a2a_combine_kernel<float><<<want, A2A_THREADS, 0, st>>>(p); break;
     default: kb::set_error("a2a: unknown dtype %d", a->dtype); return KB_ERR_ARG;
   }
   KB_CUDA_OK(cudaGetLastError());
   return KB_OK;
+}
+
+template <typename T>
+static int launch_fused(const A2aParams& p, int sms, cudaStream_t st) {
+  const size_t smem_d = (3 * p.E + 2 * MAX_ENT_PER_CTA) * sizeof(int32_t);
+  const size_t smem_e = (p.world * p.El + p.world) * sizeof(int32_t);
+  const size_t smem = smem_d > smem_e ? smem_d : smem_e;
+  int per_sm = 0;
+  KB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, a2a_fused_kernel<T>, A2A_THREADS, smem));
+  const int units = p.tok_groups * p.h_splits;
+  if (per_sm < 1 || units > per_sm * sms) {
+    kb::set_error("a2a fused: %d CTAs cannot be co-resident (%d per SM)", units, per_sm);
+    return KB_ERR_UNSUPPORTED;
+  }
+  A2aParams copy = p;
+  void* args[] = {&copy};
+  KB_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(a2a_fused_kernel<T>), dim3(units), dim3(A2A_THREADS),
+                                         args, smem, st));
+  return KB_OK;
+}
+
+extern "C" int kb_a2a_round_trip(const KbA2aArgs* a, void* stream) {
+  int sms = 0;
+  int rc = device_sms(&sms);
+  if (rc != KB_OK) return rc;
+  A2aParams p;
+  rc = fill_params(a, &p, sms);
+  if (rc != KB_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (a->dtype) {
+    case 0: return launch_fused<__nv_bfloat16>(p, sms, st);
+    case 1: return launch_fused<__half>(p, sms, st);
+    case 2: return launch_fused<float>(p, sms, st);
+  }
+  kb::set_error("a2a: unknown dtype %d", a->dtype);
+  return KB_ERR_ARG;
 }
 
 extern "C" int kb_wait_flags(const uint32_t* flags, int n, uint32_t want, uint64_t limit_ns, uint32_t* status,

@@ -40,6 +40,7 @@ constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
+constexpr int GROUP_M = 8;                   // row blocks swept together (rasterisation)
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = BN * BK * 2;
 constexpr int EPI_COLS = 128;                 // columns staged per epilogue pass
@@ -108,16 +109,38 @@ __device__ __forceinline__ Smem carve(uint8_t* raw) {
   return s;
 }
 
-// Position in this CTA's static schedule -> tile coordinates.  Row blocks are
-// visited in a rank-rotated order: RS starts just after the blocks this rank
-// owns (so they come last and every owner is fed by a different peer at any
-// time); AG starts with this rank's own rows (which need no transfer).
+// Position in the static schedule -> tile coordinates.
+//
+// Row blocks are visited in a rank-rotated sequence: RS starts just after the
+// blocks this rank owns (so they come last and every owner is fed by a
+// different peer at any time); AG starts with this rank's own rows (which need
+// no transfer).  Inside the sequence, GROUP_M consecutive row blocks form a
+// group that is swept column block by column block, so that the ~148 tiles in
+// flight share few A and B panels (L2 reuse instead of HBM re-reads).  For RS
+// the blocks this rank owns form a segment of their own at the very end: a CTA
+// never has a push queued behind one of its own waits, which is what makes
+// the cross-rank waits deadlock-free.
 __device__ __forceinline__ void tile_at(const GemmParams& p, int pos, int& mb, int& nb) {
-  int j = pos / p.NB;
-  nb = pos - j * p.NB;
   int start = 0;
-  if (p.mode == KB_GEMM_RS) start = p.own_hi_mb + 1;
+  int first_len = p.MB;  // blocks in the first segment
+  if (p.mode == KB_GEMM_RS) {
+    start = p.own_hi_mb + 1;
+    first_len = p.MB - (p.own_hi_mb - p.own_lo_mb + 1);
+  }
   if (p.mode == KB_GEMM_AG) start = p.own_lo_mb;
+  int base = 0, blocks = first_len, q = pos;
+  if (pos >= first_len * p.NB) {
+    base = first_len;
+    blocks = p.MB - first_len;
+    q = pos - first_len * p.NB;
+  }
+  const int per_group = GROUP_M * p.NB;
+  const int g = q / per_group;
+  const int r = q - g * per_group;
+  int gs = blocks - g * GROUP_M;
+  if (gs > GROUP_M) gs = GROUP_M;
+  nb = r / gs;
+  const int j = base + g * GROUP_M + (r - nb * gs);
   mb = (start + j) % p.MB;
 }
 
@@ -168,9 +191,11 @@ __device__ __forceinline__ void stage_half(uint32_t taddr, uint8_t* warp_epi, in
   }
 }
 
-template <bool kAG>
-__global__ void __launch_bounds__(kAG ? THREADS_AG : THREADS_BASE, 1)
+template <int kMode>
+__global__ void __launch_bounds__(kMode == KB_GEMM_AG ? THREADS_AG : THREADS_BASE, 1)
 gemm_kernel(const __grid_constant__ GemmParams p) {
+  constexpr bool kAG = (kMode == KB_GEMM_AG);
+  constexpr bool kRS = (kMode == KB_GEMM_RS);
   extern __shared__ uint8_t smem_raw[];
   Smem sm = carve(smem_raw);
   const int tid = threadIdx.x;
@@ -208,12 +233,12 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
-      int ready_mb = -1;
+      uint64_t ready_mask[4] = {0ull, 0ull, 0ull, 0ull};  // row blocks already seen complete
       bool ok = true;
       for (int pos = blockIdx.x; pos < total_tiles && ok; pos += gridDim.x) {
         int mb, nb;
         tile_at(p, pos, mb, nb);
-        if (kAG && mb != ready_mb) {
+        if (kAG && !(mb < 256 && ((ready_mask[mb >> 6] >> (mb & 63)) & 1ull))) {
           const int s_lo = (mb * BM) / p.rpo;
           int last_row = mb * BM + BM - 1;
           if (last_row > p.M - 1) last_row = p.M - 1;
@@ -224,7 +249,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
             }
           }
           kb::fence_proxy_async_global();
-          ready_mb = mb;
+          if (mb < 256) ready_mask[mb >> 6] |= 1ull << (mb & 63);
         }
         for (int kb_i = 0; kb_i < p.KB; ++kb_i) {
           if (!kb::mbar_wait_bounded(&sm.empty[s], ph ^ 1u, p.limit_ns)) {
@@ -292,7 +317,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     const int q = warp - 4;
     const int et = tid - 128;
     uint8_t* warp_epi = sm.epi + q * EPI_WARP_BYTES;
-    const bool rs = (p.mode == KB_GEMM_RS) && p.world > 1;
+    constexpr bool rs = kRS;  // the host maps single-rank calls to the plain kernel
     uint32_t it = 0;
     for (int pos = blockIdx.x; pos < total_tiles; pos += gridDim.x, ++it) {
       int mb, nb;
@@ -320,7 +345,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       const int tile_id = mb * p.NB + nb;
       bool released = false;
 
-      if (has_remote) {
+      if (kRS && has_remote) {
         // Phase A: rows that belong to other ranks go to their owners.
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
@@ -377,57 +402,81 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
             released = true;
           }
           __syncwarp();
-#pragma unroll 2
-          for (int i = 0; i < 16; ++i) {
-            const int row = i * 2 + (lane >> 4);
-            const int j = lane & 15;
-            const int gr = row0 + q * 32 + row;
-            const int col = nb * BN + h * EPI_COLS + j * 8;
-            if (gr < p.M && col < p.N) {
+          // Own rows: sum the peers' partials in fp32.  Loads are issued in
+          // batches of 8 rows x 4 sources per thread so that enough of them
+          // are in flight to cover the memory latency.
+          const int j = lane & 15;
+          const int col = nb * BN + h * EPI_COLS + j * 8;
+#pragma unroll 1
+          for (int hr = 0; hr < 2; ++hr) {
+            float acc[8][8];
+            int out_rows[8];
+#pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+              const int row = (hr * 8 + ii) * 2 + (lane >> 4);
+              const int gr = row0 + q * 32 + row;
+              bool mine = (gr < p.M) && (col < p.N);
               int out_row = gr;
-              bool mine = true;
               if (rs) {
-                const int owner = gr / p.rpo;
-                mine = (owner == p.rank);
+                mine = mine && (gr / p.rpo == p.rank);
                 out_row = gr - p.rank * p.rpo;
               }
-              if (mine) {
-                const uint4 v = *reinterpret_cast<const uint4*>(warp_epi + row * EPI_ROW_BYTES + ((j ^ (row & 15)) * 16));
-                float f[8];
-                {
-                  float2 t;
-                  t = kb::unpack_bf16x2(v.x); f[0] = t.x; f[1] = t.y;
-                  t = kb::unpack_bf16x2(v.y); f[2] = t.x; f[3] = t.y;
-                  t = kb::unpack_bf16x2(v.z); f[4] = t.x; f[5] = t.y;
-                  t = kb::unpack_bf16x2(v.w); f[6] = t.x; f[7] = t.y;
-                }
-                if (rs) {
-                  // Fixed summation order over sources keeps the result
-                  // bit-reproducible from run to run.
-                  for (int src = 0; src < p.world; ++src) {
-                    if (src == p.rank) continue;
-                    const uint4 u = kb::ld_sys_v4(rs_stage_row(p, p.rank, src, out_row) + col);
-                    float2 t;
-                    t = kb::unpack_bf16x2(u.x); f[0] += t.x; f[1] += t.y;
-                    t = kb::unpack_bf16x2(u.y); f[2] += t.x; f[3] += t.y;
-                    t = kb::unpack_bf16x2(u.z); f[4] += t.x; f[5] += t.y;
-                    t = kb::unpack_bf16x2(u.w); f[6] += t.x; f[7] += t.y;
+              out_rows[ii] = mine ? out_row : -1;
+              const uint4 v = *reinterpret_cast<const uint4*>(warp_epi + row * EPI_ROW_BYTES + ((j ^ (row & 15)) * 16));
+              float2 t;
+              t = kb::unpack_bf16x2(v.x); acc[ii][0] = t.x; acc[ii][1] = t.y;
+              t = kb::unpack_bf16x2(v.y); acc[ii][2] = t.x; acc[ii][3] = t.y;
+              t = kb::unpack_bf16x2(v.z); acc[ii][4] = t.x; acc[ii][5] = t.y;
+              t = kb::unpack_bf16x2(v.w); acc[ii][6] = t.x; acc[ii][7] = t.y;
+            }
+            if (rs) {
+              // Sources are visited in ascending order, so the sum is
+              // bit-reproducible from run to run.
+#pragma unroll 1
+              for (int s0 = 0; s0 < p.world; s0 += 4) {
+                uint4 u[8][4];
+#pragma unroll
+                for (int ii = 0; ii < 8; ++ii) {
+#pragma unroll
+                  for (int sj = 0; sj < 4; ++sj) {
+                    const int src = s0 + sj;
+                    u[ii][sj] = make_uint4(0u, 0u, 0u, 0u);
+                    if (out_rows[ii] >= 0 && src < p.world && src != p.rank) {
+                      u[ii][sj] = kb::ld_sys_v4(rs_stage_row(p, p.rank, src, out_rows[ii]) + col);
+                    }
                   }
                 }
-                if (p.bias != nullptr) {
-                  const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
-                  float2 t;
-                  t = kb::unpack_bf16x2(bv.x); f[0] += p.bias_scale * t.x; f[1] += p.bias_scale * t.y;
-                  t = kb::unpack_bf16x2(bv.y); f[2] += p.bias_scale * t.x; f[3] += p.bias_scale * t.y;
-                  t = kb::unpack_bf16x2(bv.z); f[4] += p.bias_scale * t.x; f[5] += p.bias_scale * t.y;
-                  t = kb::unpack_bf16x2(bv.w); f[6] += p.bias_scale * t.x; f[7] += p.bias_scale * t.y;
+#pragma unroll
+                for (int ii = 0; ii < 8; ++ii) {
+#pragma unroll
+                  for (int sj = 0; sj < 4; ++sj) {
+                    float2 t;
+                    t = kb::unpack_bf16x2(u[ii][sj].x); acc[ii][0] += t.x; acc[ii][1] += t.y;
+                    t = kb::unpack_bf16x2(u[ii][sj].y); acc[ii][2] += t.x; acc[ii][3] += t.y;
+                    t = kb::unpack_bf16x2(u[ii][sj].z); acc[ii][4] += t.x; acc[ii][5] += t.y;
+                    t = kb::unpack_bf16x2(u[ii][sj].w); acc[ii][6] += t.x; acc[ii][7] += t.y;
+                  }
                 }
+              }
+            }
+            float bz[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (p.bias != nullptr && col < p.N) {
+              const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+              float2 t;
+              t = kb::unpack_bf16x2(bv.x); bz[0] = p.bias_scale * t.x; bz[1] = p.bias_scale * t.y;
+              t = kb::unpack_bf16x2(bv.y); bz[2] = p.bias_scale * t.x; bz[3] = p.bias_scale * t.y;
+              t = kb::unpack_bf16x2(bv.z); bz[4] = p.bias_scale * t.x; bz[5] = p.bias_scale * t.y;
+              t = kb::unpack_bf16x2(bv.w); bz[6] = p.bias_scale * t.x; bz[7] = p.bias_scale * t.y;
+            }
+#pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+              if (out_rows[ii] >= 0) {
                 uint4 o;
-                o.x = kb::pack_bf16x2(f[0], f[1]);
-                o.y = kb::pack_bf16x2(f[2], f[3]);
-                o.z = kb::pack_bf16x2(f[4], f[5]);
-                o.w = kb::pack_bf16x2(f[6], f[7]);
-                *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(out_row) * p.N + col) = o;
+                o.x = kb::pack_bf16x2(acc[ii][0] + bz[0], acc[ii][1] + bz[1]);
+                o.y = kb::pack_bf16x2(acc[ii][2] + bz[2], acc[ii][3] + bz[3]);
+                o.z = kb::pack_bf16x2(acc[ii][4] + bz[4], acc[ii][5] + bz[5]);
+                o.w = kb::pack_bf16x2(acc[ii][6] + bz[6], acc[ii][7] + bz[7]);
+                *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(out_rows[ii]) * p.N + col) = o;
               }
             }
           }
@@ -633,19 +682,15 @@ extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {
   const bool ag = (p.mode == KB_GEMM_AG);
   if (!ag && grid > total_tiles) grid = total_tiles;
 
-  static bool attr_done[2] = {false, false};
-  if (ag) {
-    if (!attr_done[1]) {
-      KB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      attr_done[1] = true;
-    }
-    gemm_kernel<true><<<grid, THREADS_AG, SMEM_BYTES, stream>>>(p);
+  if (p.mode == KB_GEMM_AG) {
+    KB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<KB_GEMM_AG>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    gemm_kernel<KB_GEMM_AG><<<grid, THREADS_AG, SMEM_BYTES, stream>>>(p);
+  } else if (p.mode == KB_GEMM_RS) {
+    KB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<KB_GEMM_RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    gemm_kernel<KB_GEMM_RS><<<grid, THREADS_BASE, SMEM_BYTES, stream>>>(p);
   } else {
-    if (!attr_done[0]) {
-      KB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      attr_done[0] = true;
-    }
-    gemm_kernel<false><<<grid, THREADS_BASE, SMEM_BYTES, stream>>>(p);
+    KB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<KB_GEMM_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    gemm_kernel<KB_GEMM_PLAIN><<<grid, THREADS_BASE, SMEM_BYTES, stream>>>(p);
   }
   KB_CUDA_OK(cudaGetLastError());
   return KB_OK;

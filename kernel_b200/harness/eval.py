@@ -20,7 +20,7 @@ What differs from the reference, on purpose:
   distributed tasks (per-rank table, rank 0 reported);
 * the task is a package (``--task all2all|gemm_rs|ag_gemm``; guessed from the
   case keys otherwise), the implementation is selectable (``--impl
-  fused|baseline``) and the backend/device are parameters (``--backend
+  fused|baseline`` or ``--submission some.module``) and the backend/device are parameters (``--backend
   nccl|gloo``), so the same flow runs on CPU ranks;
 * a tests file may be replaced by ``--yaml <task.yml> --section tests|benchmarks``.
 """
@@ -83,7 +83,11 @@ class RunConfig:
         elif self.impl == "baseline":
             sub = importlib.import_module(f"kernel_b200.baseline.{self.task}")
         else:
-            raise ValueError(f"unknown impl {self.impl!r}")
+            # any importable module with a custom_kernel(data): the role of the
+            # @SUBMISSION@ placeholder in the reference's task.yml (task.yml:2)
+            sub = importlib.import_module(self.impl)
+            if not hasattr(sub, "custom_kernel"):
+                raise ValueError(f"module {self.impl!r} has no custom_kernel")
         return ref, sub
 
 
@@ -473,6 +477,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("tests_file", nargs="?")
     ap.add_argument("--task", choices=["all2all", "gemm_rs", "ag_gemm"])
     ap.add_argument("--impl", choices=["fused", "baseline"], default="fused")
+    ap.add_argument("--submission", default=None, help="module path of a custom_kernel to evaluate instead of --impl")
     ap.add_argument("--backend", choices=["nccl", "gloo"], default="nccl" if torch.cuda.is_available() else "gloo")
     ap.add_argument("--yaml")
     ap.add_argument("--section", default=None)
@@ -511,7 +516,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     with PopcornOutput(int(fd)) as logger:
         ctx = multiprocessing.get_context("spawn")
         with ctx.Pool(n_gpus) as pool:
-            runner = Runner(pool, n_gpus, ns.task, ns.impl, ns.backend)
+            runner = Runner(pool, n_gpus, ns.task, ns.submission or ns.impl, ns.backend)
             if ns.mode == "test":
                 return run_testing(logger, runner, tests)
             if ns.mode == "benchmark":

@@ -74,6 +74,7 @@ class MoEAllToAll:
             self.slots = torch.empty(self.cap, dtype=torch.int32, device=self.heap.device)
             self.status = self.heap.status
             self._eb = eb
+            self._fused = os.environ.get("KB200_A2A_FUSED", "1") == "1"
 
     # ------------------------------------------------------------- native ----
     def _args(self, x, indices, weights, out, scale_mode) -> N.A2aArgs:
@@ -118,6 +119,14 @@ class MoEAllToAll:
         a = self._args(x, indices, weights, out, scale_mode)
         lib = N.lib()
         st = torch.cuda.current_stream(x.device).cuda_stream
+        if self._fused:
+            code = lib.kb_a2a_round_trip(C.byref(a), st)
+            if code == N.KB_OK:
+                launch_count += 1
+                return out
+            if code != N.KB_ERR_UNSUPPORTED:
+                N.check(code)
+            self._fused = False  # too many CTAs for one cooperative launch: three launches
         N.check(lib.kb_a2a_dispatch(C.byref(a), st))
         N.check(lib.kb_a2a_expert_scale(C.byref(a), st))
         N.check(lib.kb_a2a_combine(C.byref(a), st))

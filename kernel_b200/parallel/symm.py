@@ -71,7 +71,8 @@ class SymmHeap:
         if backend not in _BACKENDS:
             raise ValueError(f"unknown symmetric-memory backend {backend!r}")
         if backend != "host":
-            if device is None:
+            device = torch.device("cuda") if device is None else torch.device(device)
+            if device.index is None:
                 device = torch.device("cuda", torch.cuda.current_device())
             torch.cuda.set_device(device)
         self.device = torch.device("cpu") if backend == "host" else torch.device(device)

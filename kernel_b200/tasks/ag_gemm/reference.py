@@ -66,8 +66,23 @@ def ref_kernel(data: input_t) -> output_t:
     return out.to(torch.bfloat16)
 
 
+def ref_kernel_fp32(data: input_t) -> torch.Tensor:
+    """Collective oracle computed in fp32."""
+    a_local, w, bias = data
+    world = _world()
+    if world > 1:
+        a = torch.empty((a_local.shape[0] * world, a_local.shape[1]), dtype=a_local.dtype, device=a_local.device)
+        dist.all_gather_into_tensor(a, a_local.contiguous())
+    else:
+        a = a_local
+    out = a.float() @ w.float().t()
+    if bias is not None:
+        out = out + bias.float()
+    return out
+
+
 def check_implementation(data: input_t, output: output_t):
-    expected = ref_kernel(data)
+    expected = ref_kernel_fp32(data)
     if output.device != expected.device:
         return False, f"Output device mismatch: {output.device} != {expected.device}"
     if output.shape != expected.shape:

@@ -1,0 +1,97 @@
+"""The evaluator's command line, protocol and exit codes, on CPU/gloo ranks."""
+import base64
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+
+A2A = ("num_experts: 8; experts_per_token: 2; hidden_dim: 256; max_num_tokens: 64; seed: 5; world_size: 2; "
+       "dtype: fp32; fixed_tokens: True; weight_mode: softmax; expert_scale: identity")
+RS = "world_size: 2; m: 64; n: 128; k: 256; has_bias: False; seed: 3"
+AG = "world_size: 2; m: 64; n: 128; k: 256; has_bias: True; seed: 3; op: ag_gemm"
+
+
+def _run(args, tests_text, tmp_path, env_extra=None, with_fd=True):
+    tests = tmp_path / "tests.txt"
+    tests.write_text(tests_text)
+    r, w = os.pipe()
+    env = dict(os.environ, POPCORN_GPUS="2", PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
+    env.pop("POPCORN_FD", None)
+    env.pop("MASTER_PORT", None)
+    if with_fd:
+        env["POPCORN_FD"] = str(w)
+    env.update(env_extra or {})
+    argv = [sys.executable, "-m", "kernel_b200.harness.eval"] + [a if a != "@tests" else str(tests) for a in args]
+    proc = subprocess.run(argv, env=env, pass_fds=(w,), cwd=ROOT, capture_output=True, text=True, timeout=600)
+    os.close(w)
+    with os.fdopen(r) as f:
+        out = f.read()
+    log = dict(line.split(": ", 1) for line in out.splitlines() if ": " in line)
+    return proc.returncode, log, proc.stderr
+
+
+def test_test_mode_passes_on_gloo(tmp_path):
+    rc, log, err = _run(["test", "@tests", "--backend", "gloo"], "\n".join([A2A, RS, AG]) + "\n", tmp_path)
+    assert rc == 0, err
+    assert log["test-count"] == "3" and log["check"] == "pass"
+    assert [log[f"test.{i}.status"] for i in range(3)] == ["pass"] * 3
+    assert log["test.1.spec"] == RS
+
+
+def test_baseline_impl_and_secret_seed(tmp_path):
+    rc, log, err = _run(["test", "@tests", "--backend", "gloo", "--impl", "baseline"], A2A + "\n" + RS + "\n", tmp_path,
+                        env_extra={"POPCORN_SEED": "987654321"})
+    assert rc == 0, err
+    assert log["check"] == "pass"
+
+
+def test_benchmark_mode_reports_stats(tmp_path):
+    rc, log, err = _run(["benchmark", "@tests", "--backend", "gloo"], RS + "\n", tmp_path)
+    assert rc == 0, err
+    assert log["benchmark-count"] == "1" and log["check"] == "pass"
+    for key in ("runs", "mean", "std", "err", "best", "worst", "max_rank_us"):
+        assert f"benchmark.0.{key}" in log
+    assert 3 <= int(log["benchmark.0.runs"]) <= 100
+    assert float(log["benchmark.0.best"]) <= float(log["benchmark.0.mean"]) <= float(log["benchmark.0.worst"])
+
+
+def test_profile_mode_is_distributed_aware(tmp_path):
+    rc, log, err = _run(["profile", "@tests", "--backend", "gloo"], RS + "\n", tmp_path)
+    assert rc == 0, err
+    table = base64.b64decode(log["benchmark.0.report"], b"+*").decode()
+    assert "Self CPU" in table
+
+
+def test_exit_codes(tmp_path):
+    assert _run(["test", "@tests"], RS + "\n", tmp_path, with_fd=False)[0] == 111      # no POPCORN_FD
+    assert _run(["test"], RS + "\n", tmp_path)[0] == 2                                  # missing tests file
+    assert _run(["frobnicate", "@tests"], RS + "\n", tmp_path)[0] == 2                  # unknown mode
+    assert _run(["test", "@tests", "--backend", "gloo"], "m 64\n", tmp_path)[0] == 113  # malformed case
+    assert _run(["test", str(tmp_path / "missing.txt")], "", tmp_path)[0] == 113        # unreadable file
+
+
+def test_world_larger_than_pool_fails_fast(tmp_path):
+    rc, log, err = _run(["test", "@tests", "--backend", "gloo"], RS.replace("world_size: 2", "world_size: 4") + "\n", tmp_path)
+    assert rc == 112
+    assert log["test.0.status"] == "fail" and "exceeds" in log["test.0.error"]
+
+
+def test_wrong_submission_is_reported(tmp_path):
+    (tmp_path / "wrong_sub.py").write_text(
+        "from kernel_b200.tasks.gemm_rs.submission import custom_kernel as good\n"
+        "def custom_kernel(data):\n    return good(data) + 1.0\n")
+    case = "world_size: 2; m: 64; n: 128; k: 256; has_bias: True; seed: 3; dist: normal"
+    rc, log, err = _run(["test", "@tests", "--backend", "gloo", "--submission", "wrong_sub"], case + "\n", tmp_path,
+                        env_extra={"PYTHONPATH": f"{ROOT}:{tmp_path}"})
+    assert rc == 112 and log["check"] == "fail" and "mismatch" in log["test.0.error"]
+    assert "rank 0" in log["test.0.error"]
+
+
+def test_yaml_input_with_world_override(tmp_path):
+    yml = tmp_path / "task.yml"
+    yml.write_text('tests:\n  - {"world_size": 8, "m": 64, "n": 128, "k": 256, "has_bias": True, "seed": 1}\n')
+    rc, log, err = _run(["test", "--yaml", str(yml), "--world", "2", "--backend", "gloo", "--task", "gemm_rs"], "", tmp_path)
+    assert rc == 0, err
+    assert log["check"] == "pass"

@@ -1,0 +1,163 @@
+"""The three fused ops across GPUs (one process per GPU, NCCL as control plane
+only), checked with the tasks' own oracles.  Needs at least two GPUs."""
+import pytest
+import torch
+
+from _mp import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _world():
+    n = torch.cuda.device_count()
+    return 8 if n >= 8 else (4 if n >= 4 else 2)
+
+
+def _a2a(rank, world, specs):
+    import torch
+
+    from kernel_b200.tasks.all2all import reference as R
+    from kernel_b200.tasks.all2all import submission as S
+
+    res = []
+    for spec in specs:
+        data = R.generate_input(**spec, rank=rank, world_size=world)
+        out1 = S.custom_kernel(data)
+        out2 = S.custom_kernel(data)
+        torch.cuda.synchronize()
+        ctx = S.get_context(data[0], world, data[1].x.device)
+        ctx.heap.check_status()
+        ok, msg = R.check_implementation(data, out1)
+        closed = torch.allclose(out1.float(), R.ref_closed_form(data).float(), rtol=1e-2, atol=5e-3)
+        res.append((ok, msg, bool(closed), bool(torch.equal(out1, out2))))
+    S.release_contexts()
+    return res
+
+
+def test_all2all_task_cases():
+    world = _world()
+    specs = [
+        dict(num_experts=8, experts_per_token=2, hidden_dim=6144, max_num_tokens=4, seed=1236),
+        dict(num_experts=64, experts_per_token=6, hidden_dim=2048, max_num_tokens=8, seed=542),
+        dict(num_experts=128, experts_per_token=4, hidden_dim=2880, max_num_tokens=32, seed=51),
+        dict(num_experts=256, experts_per_token=8, hidden_dim=7168, max_num_tokens=128, seed=4),
+        dict(num_experts=256, experts_per_token=8, hidden_dim=7168, max_num_tokens=256, seed=11, dtype="bf16",
+             fixed_tokens=True, weight_mode="softmax", expert_scale="expert"),
+        dict(num_experts=8, experts_per_token=2, hidden_dim=256, max_num_tokens=64, seed=3, dtype="fp32",
+             fixed_tokens=True, weight_mode="softmax", expert_scale="identity"),
+    ]
+    for per_rank in run_ranks(_a2a, world, specs, backend="nccl", timeout=300):
+        for ok, msg, closed, repeat in per_rank:
+            assert ok, msg
+            assert closed and repeat
+
+
+def _gemm_rs(rank, world, shapes):
+    import torch
+
+    from kernel_b200.tasks.gemm_rs import reference as R
+    from kernel_b200.tasks.gemm_rs import submission as S
+
+    res = []
+    for (m, n, k, bias, dist_mode, bias_mode) in shapes:
+        data = R.generate_input(rank, world, m, n, k, bias, seed=7, dist=dist_mode, bias_mode=bias_mode)
+        out1 = S.custom_kernel(data)
+        out2 = S.custom_kernel(data)
+        torch.cuda.synchronize()
+        ctx = S.get_context(m, n, data[0].device)
+        if ctx.heap is not None:
+            ctx.heap.check_status()
+        ok, msg = R.check_implementation(data, out1)
+        res.append((ok, msg, bool(torch.equal(out1, out2)), tuple(out1.shape) == (m // world, n)))
+    S.release_contexts()
+    return res
+
+
+def test_gemm_rs_task_shapes():
+    world = _world()
+    shapes = [
+        (64, 2880, 2880 // 8 * world, True, "uniform", "per_rank"),   # rows per rank < tile: row-granular ownership
+        (512, 3584, 14336 // 8 * world, True, "normal", "once"),
+        (2048, 4096, 7168 // 8 * world, False, "normal", "once"),
+        (4096, 2880, 2880 // 8 * world, True, "normal", "per_rank"),
+        (8192, 8192, 29568 // 8 * world, True, "normal", "once"),     # K_local 3696: K tail of 48
+    ]
+    for per_rank in run_ranks(_gemm_rs, world, shapes, backend="nccl", timeout=300):
+        for ok, msg, repeat, shape_ok in per_rank:
+            assert ok, msg
+            assert repeat and shape_ok
+
+
+def _ag_gemm(rank, world, shapes):
+    import torch
+
+    from kernel_b200.tasks.ag_gemm import reference as R
+    from kernel_b200.tasks.ag_gemm import submission as S
+
+    res = []
+    for (m, n, k, bias) in shapes:
+        data = R.generate_input(rank, world, m, n, k, bias, seed=9)
+        out1 = S.custom_kernel(data)
+        out2 = S.custom_kernel(data)
+        torch.cuda.synchronize()
+        ctx = S.get_context(m, k, data[0].device)
+        if ctx.heap is not None:
+            ctx.heap.check_status()
+        ok, msg = R.check_implementation(data, out1)
+        res.append((ok, msg, bool(torch.equal(out1, out2))))
+    S.release_contexts()
+    return res
+
+
+def test_ag_gemm_shapes():
+    world = _world()
+    shapes = [
+        (64, 2880 * world // 8 * 8, 2880, True),   # rows per rank < tile: several sources per row block
+        (1024, 4096, 4096, False),
+        (4096, 2880 * world, 2880, True),
+        (8192, 3696 * world, 8192, True),           # N_local 3696: N tail of 112
+    ]
+    for per_rank in run_ranks(_ag_gemm, world, shapes, backend="nccl", timeout=300):
+        for ok, msg, repeat in per_rank:
+            assert ok, msg
+            assert repeat
+
+
+def _rank_leaves(rank, world):
+    """A rank leaves between steps (nothing in flight); the others learn of it
+    from the host-side store before their next launch."""
+    import datetime
+
+    import torch
+    import torch.distributed as dist
+
+    from kernel_b200.ops.gemm import GemmRS
+
+    dev = torch.device("cuda", rank)
+    ctx = GemmRS(256, 512, device=dev)
+    a = torch.randn(256, 64, device=dev).to(torch.bfloat16)
+    w = torch.randn(512, 64, device=dev).to(torch.bfloat16)
+    ctx(a, w)
+    torch.cuda.synchronize()
+    ctx.heap.check_status()
+    store = dist.distributed_c10d._get_default_store()
+    store.set(f"alive/{rank}", "1")
+    dist.barrier()
+    if rank == world - 1:
+        store.set(f"alive/{rank}", "0")  # announces its departure, then stops taking part
+        left = True
+    else:
+        left = False
+    dist.barrier()
+    gone = [r for r in range(world) if store.get(f"alive/{r}") == b"0"]
+    if not left and not gone:
+        ctx(a, w)  # would only run if everybody were still there
+    dist.barrier()
+    ctx.heap.close()
+    return gone
+
+
+def test_departed_rank_is_seen_on_the_host_before_the_next_launch(monkeypatch):
+    world = 2
+    res = run_ranks(_rank_leaves, world, backend="nccl", timeout=120, env={"NCCL_NVLS_ENABLE": "0"})
+    assert all(gone == [world - 1] for gone in res)
