@@ -171,7 +171,8 @@ __device__ __forceinline__ void comm_bar_sync() { asm volatile("bar.sync 2, 128;
 // TMEM -> bf16 -> this warp's 32 x 128 staging rows (16-byte chunks XOR-swizzled
 // by row so both the row-per-thread writes and the row-contiguous reads are
 // bank-conflict free).
-__device__ __forceinline__ void stage_half(uint32_t taddr, uint8_t* warp_epi, int lane) {
+__device__ __forceinline__ void stage_half(uint32_t taddr, uint8_t* warp_epi, int lane, const bf16* bias = nullptr,
+                                           float bias_scale = 1.f, int col0 = 0, int n_cols = 0) {
 #pragma unroll
   for (int c = 0; c < EPI_COLS / 32; ++c) {
     uint32_t r[32];
@@ -179,16 +180,71 @@ __device__ __forceinline__ void stage_half(uint32_t taddr, uint8_t* warp_epi, in
     kb::tmem_ld_wait();
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * i + e]);
+      if (bias != nullptr) {
+        // Added in fp32 before the single rounding to bf16.  All lanes read
+        // the same 16 bytes (they hold different rows of the same columns).
+        const int col = col0 + c * 32 + i * 8;
+        if (col < n_cols) {
+          const uint4 bv = *reinterpret_cast<const uint4*>(bias + col);
+          float2 t;
+          t = kb::unpack_bf16x2(bv.x); f[0] += bias_scale * t.x; f[1] += bias_scale * t.y;
+          t = kb::unpack_bf16x2(bv.y); f[2] += bias_scale * t.x; f[3] += bias_scale * t.y;
+          t = kb::unpack_bf16x2(bv.z); f[4] += bias_scale * t.x; f[5] += bias_scale * t.y;
+          t = kb::unpack_bf16x2(bv.w); f[6] += bias_scale * t.x; f[7] += bias_scale * t.y;
+        }
+      }
       uint4 v;
-      v.x = kb::pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
-      v.y = kb::pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-      v.z = kb::pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-      v.w = kb::pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+      v.x = kb::pack_bf16x2(f[0], f[1]);
+      v.y = kb::pack_bf16x2(f[2], f[3]);
+      v.z = kb::pack_bf16x2(f[4], f[5]);
+      v.w = kb::pack_bf16x2(f[6], f[7]);
       const int j = c * 4 + i;
       const int phys = j ^ (lane & 15);
       *reinterpret_cast<uint4*>(warp_epi + lane * EPI_ROW_BYTES + phys * 16) = v;
     }
   }
+}
+
+// TMEM -> fp32 -> this warp's 32 x 64 staging rows (256 bytes per row, same XOR
+// swizzle of the 16-byte chunks).
+__device__ __forceinline__ void stage_quarter_f32(uint32_t taddr, uint8_t* warp_epi, int lane) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t r[32];
+    kb::tmem_ld_32x32(taddr + c * 32, r);
+    kb::tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint4 v = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+      const int j = c * 8 + i;
+      *reinterpret_cast<uint4*>(warp_epi + lane * EPI_ROW_BYTES + ((j ^ (lane & 15)) * 16)) = v;
+    }
+  }
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  float2 t;
+  t = kb::unpack_bf16x2(v.x); f[0] = t.x; f[1] = t.y;
+  t = kb::unpack_bf16x2(v.y); f[2] = t.x; f[3] = t.y;
+  t = kb::unpack_bf16x2(v.z); f[4] = t.x; f[5] = t.y;
+  t = kb::unpack_bf16x2(v.w); f[6] = t.x; f[7] = t.y;
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 o;
+  o.x = kb::pack_bf16x2(f[0], f[1]);
+  o.y = kb::pack_bf16x2(f[2], f[3]);
+  o.z = kb::pack_bf16x2(f[4], f[5]);
+  o.w = kb::pack_bf16x2(f[6], f[7]);
+  return o;
+}
+__device__ __forceinline__ void load_bias8(const bf16* b, float scale, float* out) {
+  const uint4 bv = *reinterpret_cast<const uint4*>(b);
+  unpack8(bv, out);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) out[e] *= scale;
 }
 
 template <int kMode>
@@ -392,95 +448,99 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           }
           epi_bar_sync();
         }
+        if constexpr (!kRS) {
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-          stage_half(taddr + h * EPI_COLS, warp_epi, lane);
-          if (h == 1) {
-            kb::tc_fence_before_sync();
+          for (int h = 0; h < 2; ++h) {
+            stage_half(taddr + h * EPI_COLS, warp_epi, lane, p.bias, p.bias_scale, nb * BN + h * EPI_COLS, p.N);
+            if (h == 1) {
+              kb::tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) kb::mbar_arrive(&sm.tempty[acc]);
+              released = true;
+            }
             __syncwarp();
-            if (lane == 0) kb::mbar_arrive(&sm.tempty[acc]);
-            released = true;
+            const int j = lane & 15;
+            const int col = nb * BN + h * EPI_COLS + j * 8;
+#pragma unroll 4
+            for (int i = 0; i < 16; ++i) {
+              const int row = i * 2 + (lane >> 4);
+              const int gr = row0 + q * 32 + row;
+              if (gr < p.M && col < p.N) {
+                const uint4 v = *reinterpret_cast<const uint4*>(warp_epi + row * EPI_ROW_BYTES + ((j ^ (row & 15)) * 16));
+                *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(gr) * p.N + col) = v;
+              }
+            }
+            __syncwarp();
           }
-          __syncwarp();
-          // Own rows: sum the peers' partials in fp32.  Loads are issued in
-          // batches of 8 rows x 4 sources per thread so that enough of them
-          // are in flight to cover the memory latency.
-          const int j = lane & 15;
-          const int col = nb * BN + h * EPI_COLS + j * 8;
+        } else {
+          // Own rows of a reduce-scatter tile.  The local accumulator stays in
+          // fp32 (staged 64 columns at a time); the peers' bf16 partials are
+          // added in ascending source order, so the sum is bit-reproducible.
+          // Loads are issued in batches of 8 rows x 4 sources per thread so
+          // that enough of them are in flight to cover the memory latency.
 #pragma unroll 1
-          for (int hr = 0; hr < 2; ++hr) {
-            float acc[8][8];
+          for (int qd = 0; qd < 4; ++qd) {
+            stage_quarter_f32(taddr + qd * 64, warp_epi, lane);
+            if (qd == 3) {
+              kb::tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) kb::mbar_arrive(&sm.tempty[acc]);
+              released = true;
+            }
+            __syncwarp();
+            const int c8 = lane & 7;
+            const int col = nb * BN + qd * 64 + c8 * 8;
+            float accv[8][8];
             int out_rows[8];
 #pragma unroll
             for (int ii = 0; ii < 8; ++ii) {
-              const int row = (hr * 8 + ii) * 2 + (lane >> 4);
+              const int row = ii * 4 + (lane >> 3);
               const int gr = row0 + q * 32 + row;
-              bool mine = (gr < p.M) && (col < p.N);
-              int out_row = gr;
-              if (rs) {
-                mine = mine && (gr / p.rpo == p.rank);
-                out_row = gr - p.rank * p.rpo;
-              }
-              out_rows[ii] = mine ? out_row : -1;
-              const uint4 v = *reinterpret_cast<const uint4*>(warp_epi + row * EPI_ROW_BYTES + ((j ^ (row & 15)) * 16));
-              float2 t;
-              t = kb::unpack_bf16x2(v.x); acc[ii][0] = t.x; acc[ii][1] = t.y;
-              t = kb::unpack_bf16x2(v.y); acc[ii][2] = t.x; acc[ii][3] = t.y;
-              t = kb::unpack_bf16x2(v.z); acc[ii][4] = t.x; acc[ii][5] = t.y;
-              t = kb::unpack_bf16x2(v.w); acc[ii][6] = t.x; acc[ii][7] = t.y;
+              const bool mine = (gr < p.M) && (col < p.N) && (gr / p.rpo == p.rank);
+              out_rows[ii] = mine ? gr - p.rank * p.rpo : -1;
+              const uint8_t* rowp = warp_epi + row * EPI_ROW_BYTES;
+              const float4 lo = *reinterpret_cast<const float4*>(rowp + (((2 * c8) ^ (row & 15)) * 16));
+              const float4 hi = *reinterpret_cast<const float4*>(rowp + (((2 * c8 + 1) ^ (row & 15)) * 16));
+              accv[ii][0] = lo.x; accv[ii][1] = lo.y; accv[ii][2] = lo.z; accv[ii][3] = lo.w;
+              accv[ii][4] = hi.x; accv[ii][5] = hi.y; accv[ii][6] = hi.z; accv[ii][7] = hi.w;
             }
-            if (rs) {
-              // Sources are visited in ascending order, so the sum is
-              // bit-reproducible from run to run.
 #pragma unroll 1
-              for (int s0 = 0; s0 < p.world; s0 += 4) {
-                uint4 u[8][4];
+            for (int s0 = 0; s0 < p.world; s0 += 4) {
+              uint4 u[8][4];
 #pragma unroll
-                for (int ii = 0; ii < 8; ++ii) {
+              for (int ii = 0; ii < 8; ++ii) {
 #pragma unroll
-                  for (int sj = 0; sj < 4; ++sj) {
-                    const int src = s0 + sj;
-                    u[ii][sj] = make_uint4(0u, 0u, 0u, 0u);
-                    if (out_rows[ii] >= 0 && src < p.world && src != p.rank) {
-                      u[ii][sj] = kb::ld_sys_v4(rs_stage_row(p, p.rank, src, out_rows[ii]) + col);
-                    }
+                for (int sj = 0; sj < 4; ++sj) {
+                  const int src = s0 + sj;
+                  u[ii][sj] = make_uint4(0u, 0u, 0u, 0u);
+                  if (out_rows[ii] >= 0 && src < p.world && src != p.rank) {
+                    u[ii][sj] = kb::ld_sys_v4(rs_stage_row(p, p.rank, src, out_rows[ii]) + col);
                   }
                 }
+              }
 #pragma unroll
-                for (int ii = 0; ii < 8; ++ii) {
+              for (int ii = 0; ii < 8; ++ii) {
 #pragma unroll
-                  for (int sj = 0; sj < 4; ++sj) {
-                    float2 t;
-                    t = kb::unpack_bf16x2(u[ii][sj].x); acc[ii][0] += t.x; acc[ii][1] += t.y;
-                    t = kb::unpack_bf16x2(u[ii][sj].y); acc[ii][2] += t.x; acc[ii][3] += t.y;
-                    t = kb::unpack_bf16x2(u[ii][sj].z); acc[ii][4] += t.x; acc[ii][5] += t.y;
-                    t = kb::unpack_bf16x2(u[ii][sj].w); acc[ii][6] += t.x; acc[ii][7] += t.y;
-                  }
+                for (int sj = 0; sj < 4; ++sj) {
+                  float f[8];
+                  unpack8(u[ii][sj], f);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) accv[ii][e] += f[e];
                 }
               }
             }
             float bz[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (p.bias != nullptr && col < p.N) {
-              const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
-              float2 t;
-              t = kb::unpack_bf16x2(bv.x); bz[0] = p.bias_scale * t.x; bz[1] = p.bias_scale * t.y;
-              t = kb::unpack_bf16x2(bv.y); bz[2] = p.bias_scale * t.x; bz[3] = p.bias_scale * t.y;
-              t = kb::unpack_bf16x2(bv.z); bz[4] = p.bias_scale * t.x; bz[5] = p.bias_scale * t.y;
-              t = kb::unpack_bf16x2(bv.w); bz[6] = p.bias_scale * t.x; bz[7] = p.bias_scale * t.y;
-            }
+            if (p.bias != nullptr && col < p.N) load_bias8(p.bias + col, p.bias_scale, bz);
 #pragma unroll
             for (int ii = 0; ii < 8; ++ii) {
               if (out_rows[ii] >= 0) {
-                uint4 o;
-                o.x = kb::pack_bf16x2(acc[ii][0] + bz[0], acc[ii][1] + bz[1]);
-                o.y = kb::pack_bf16x2(acc[ii][2] + bz[2], acc[ii][3] + bz[3]);
-                o.z = kb::pack_bf16x2(acc[ii][4] + bz[4], acc[ii][5] + bz[5]);
-                o.w = kb::pack_bf16x2(acc[ii][6] + bz[6], acc[ii][7] + bz[7]);
-                *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(out_rows[ii]) * p.N + col) = o;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) accv[ii][e] += bz[e];
+                *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(out_rows[ii]) * p.N + col) = pack8(accv[ii]);
               }
             }
+            __syncwarp();
           }
-          __syncwarp();
         }
       }
       if (!released) {
