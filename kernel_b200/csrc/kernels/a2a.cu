@@ -608,3 +608,101 @@ extern "C" int kb_device_barrier(void* const* peer_bases, uint64_t pad_off, int 
   KB_CUDA_OK(cudaGetLastError());
   return KB_OK;
 }
+
+// ------------------------------------------------- allocation-free entry point ----
+// See a2a_static.h.  The workspace lives in a file-scope device array; host code
+// must not pass the array's name to a kernel (on the host it is only a stand-in
+// for the symbol), so its device address is looked up once per device.
+#include "a2a_static.h"
+
+static __device__ __align__(256) unsigned char g_a2a_static_scratch[KB_A2A_STATIC_BYTES];
+
+namespace {
+struct StaticSlot {
+  unsigned char* base = nullptr;
+  uint32_t epoch = 0;
+};
+StaticSlot g_static_slots[64];
+}  // namespace
+
+extern "C" int kb_a2a_round_trip_static(const void* x, const int32_t* indices, const float* weights, void* out,
+                                        int num_tokens, int num_experts, int topk, int hidden, int dtype,
+                                        int scale_mode, void* stream) {
+  const int elem_bytes = (dtype == 2) ? 4 : 2;
+  if (dtype < 0 || dtype > 2 || x == nullptr || indices == nullptr || weights == nullptr || out == nullptr) {
+    kb::set_error("a2a static: null pointer or unknown dtype %d", dtype);
+    return KB_ERR_ARG;
+  }
+  if (num_tokens < 0 || topk <= 0 || hidden <= 0 || num_experts <= 0) {
+    kb::set_error("a2a static: sizes must be positive");
+    return KB_ERR_ARG;
+  }
+  const unsigned long long rows = static_cast<unsigned long long>(num_tokens > 0 ? num_tokens : 1) * topk;
+  const unsigned long long row_bytes = rows * hidden * elem_bytes;
+  if (row_bytes > KB_A2A_STATIC_ROW_BYTES || rows > KB_A2A_STATIC_MAX_ROWS || num_experts > KB_A2A_STATIC_MAX_EXPERTS) {
+    kb::set_error(
+        "a2a static: request exceeds the built-in workspace (tokens*topk*hidden*elem = %llu > %u bytes, or rows %llu > %d, "
+        "or experts %d > %d); use the regular entry points with an allocated workspace",
+        row_bytes, KB_A2A_STATIC_ROW_BYTES, rows, KB_A2A_STATIC_MAX_ROWS, num_experts, KB_A2A_STATIC_MAX_EXPERTS);
+    return KB_ERR_ARG;
+  }
+  int dev = 0;
+  KB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    kb::set_error("a2a static: device index %d out of range", dev);
+    return KB_ERR_ARG;
+  }
+  StaticSlot& slot = g_static_slots[dev];
+  if (slot.base == nullptr) {
+    // Set-up, once per device, with that device current.
+    unsigned char* ptr = nullptr;
+    KB_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_a2a_static_scratch));
+    slot.base = ptr;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  // Layout inside the array (all offsets multiples of 256).
+  const uint64_t recv_off = 0;
+  const uint64_t y_off = KB_A2A_STATIC_ROW_BYTES;
+  const uint64_t slots_off = 2ull * KB_A2A_STATIC_ROW_BYTES;
+  const uint64_t count_off = slots_off + 4ull * KB_A2A_STATIC_MAX_ROWS;
+  const uint64_t flag_off = count_off + 4ull * KB_A2A_STATIC_MAX_EXPERTS;
+  const uint64_t sync_off = flag_off + 256;
+  const uint64_t status_off = sync_off + 256;
+
+  // The block counters must start at zero (a call that was cut short could have
+  // left them elsewhere); the status words are cleared for this call.
+  KB_CUDA_OK(cudaMemsetAsync(slot.base + sync_off, 0, 512, st));
+
+  KbA2aArgs a;
+  memset(&a, 0, sizeof(a));
+  a.rank = 0;
+  a.world = 1;
+  a.num_experts = num_experts;
+  a.topk = topk;
+  a.hidden = hidden;
+  a.max_tokens = num_tokens > 0 ? num_tokens : 1;
+  a.num_tokens = num_tokens;
+  a.elem_bytes = elem_bytes;
+  a.dtype = dtype;
+  a.x = x;
+  a.indices = indices;
+  a.weights = weights;
+  a.out = out;
+  a.slots = reinterpret_cast<int32_t*>(slot.base + slots_off);
+  a.epoch = ++slot.epoch;  // flags keep the previous call's epoch; epochs only grow
+  a.peer_base[0] = slot.base;
+  a.recv_off = recv_off;
+  a.y_off = y_off;
+  a.count_off = count_off;
+  a.flag_off = flag_off;
+  a.sync_off = sync_off;
+  a.scale_mode = scale_mode;
+  a.status = reinterpret_cast<uint32_t*>(slot.base + status_off);
+  a.wait_limit_ns = 2000000000ull;
+  int rc = kb_a2a_dispatch(&a, st);
+  if (rc != KB_OK) return rc;
+  rc = kb_a2a_expert_scale(&a, st);
+  if (rc != KB_OK) return rc;
+  return kb_a2a_combine(&a, st);
+}
