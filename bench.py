@@ -179,7 +179,7 @@ class OursArm:
         rd.num_tokens, rd.x, rd.indices, rd.weights = x.shape[0], x, idx, w
         return rd
 
-    def a2a_call(self, x, idx, w):
+    def a2a_call(self, x, idx, w, fresh_inputs=False):
         return self.a2a.custom_kernel((self.cfg, self._rank_data(x, idx, w), self.rank, self.world))
 
     def rs_call(self, a, w, b):
@@ -226,7 +226,12 @@ class ReferenceArm:
         self.rs_ref, self.rs_sub = load(ref_root / "gemm_rs")
         self.cfg = self.a2a_ref.MoEConfig(**A2A, in_dtype=torch.bfloat16, out_dtype=torch.bfloat16)
 
-    def a2a_call(self, x, idx, w):
+    def a2a_call(self, x, idx, w, fresh_inputs=False):
+        if fresh_inputs:
+            # The reference's custom_kernel works on side streams that do not wait
+            # for the stream that produced its inputs (submission.py:16-17,199-201);
+            # inputs that were just copied in must have landed before it is called.
+            torch.cuda.current_stream().synchronize()
         rd = object.__new__(self.a2a_ref.RankTestData)
         rd.num_tokens, rd.x, rd.indices, rd.weights = x.shape[0], x, idx, w
         return self.a2a_sub.custom_kernel((self.cfg, rd, self.rank, self.world))
@@ -279,7 +284,7 @@ def run(args):
         # custom_kernel, device -> host copy of the result: all inside the events.
         if name == "a2a":
             out = arm.a2a_call(host["x"].to(dev, non_blocking=True), host["idx"].to(dev, non_blocking=True),
-                               host["w"].to(dev, non_blocking=True))
+                               host["w"].to(dev, non_blocking=True), fresh_inputs=True)
         elif name == "gemm_rs":
             out = arm.rs_call(host["a_rs"].to(dev, non_blocking=True), d["w_rs"], d["b_rs"])
         else:

@@ -94,9 +94,11 @@ def ref_fp32(all_inputs, all_weights, bias, rank: int, bias_mode: str = "once") 
     return acc[rank * rows:(rank + 1) * rows]
 
 
-def ref_kernel_fp32(data: input_t) -> torch.Tensor:
+def ref_kernel_fp32(data: input_t, with_magnitude: bool = False):
     """Collective oracle with fp32 partial products and an fp32 reduction: the
-    value both the fused kernel and the bf16 library path approximate."""
+    value both the fused kernel and the bf16 library path approximate.  With
+    ``with_magnitude`` it also returns ``sum_r |partial_r| (+ |bias|)``, the scale
+    of the rounding error of any summation of the partials."""
     a, w, bias = data
     world = _world()
     M, N = a.shape[0], w.shape[0]
@@ -106,22 +108,42 @@ def ref_kernel_fp32(data: input_t) -> torch.Tensor:
         dist.reduce_scatter_tensor(rs, part)
     else:
         rs = part
+    mag = None
+    if with_magnitude:
+        if world > 1:
+            mag = torch.empty_like(rs)
+            dist.reduce_scatter_tensor(mag, part.abs())
+        else:
+            mag = part.abs()
     if bias is not None:
-        rs = rs + (world if task.get_bias_mode() == "per_rank" else 1) * bias.float()
-    return rs
+        scale = world if task.get_bias_mode() == "per_rank" else 1
+        rs = rs + scale * bias.float()
+        if mag is not None:
+            mag = mag + scale * bias.float().abs()
+    return (rs, mag) if with_magnitude else rs
 
 
 def check_implementation(data: input_t, output: output_t):
-    """Collective.  Compares against the fp32 oracle: the bf16 library path
-    (``ref_kernel``) rounds after every hop of the reduction and is itself up to
-    a few bf16 ulps away from the exact sum, which is more than the tolerance
-    when the values are O(1)."""
-    expected = ref_kernel_fp32(data)
+    """Collective.  ``|output - exact| <= atol + rtol * sum_r |partial_r|`` against
+    the fp32 oracle.
+
+    The reference compares with its bf16 library path at ``rtol = atol = 1e-2``
+    relative to the result (``gemm_rs/reference.py:67``), which its own +-0.01
+    inputs never stress.  With O(1) values every rank's partial is rounded to bf16
+    before the sum, so the error of a correct implementation scales with the
+    partials, not with the (possibly cancelling) result: measured against fp32 the
+    library path misses the result-relative bound on tens of elements per rank.
+    The bound used here is the standard forward-error bound of a summation with
+    the same two constants; for one rank it is the reference's bound exactly."""
+    expected, magnitude = ref_kernel_fp32(data, with_magnitude=True)
     if output.device != expected.device:
         return False, f"Output device mismatch: {output.device} != {expected.device}"
     if output.shape != expected.shape:
         return False, f"Output shape mismatch: {tuple(output.shape)} != {tuple(expected.shape)}"
-    if not torch.allclose(output.float(), expected.float(), rtol=RTOL, atol=ATOL):
-        diff = (output.float() - expected.float()).abs()
-        return False, f"Output values mismatch: max abs diff {diff.max().item():.5g}"
+    diff = (output.float() - expected).abs()
+    bad = ~(diff <= ATOL + RTOL * magnitude)  # also catches NaN
+    if bool(bad.any()):
+        i = int(diff.argmax())
+        return False, (f"Output values mismatch: {int(bad.sum())} of {bad.numel()} elements, max abs diff "
+                       f"{diff.max().item():.5g} at flat index {i} (expected {expected.flatten()[i].item():.5g})")
     return True, ""

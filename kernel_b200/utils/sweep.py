@@ -79,14 +79,18 @@ def main() -> int:
                 ts.append(e0.elapsed_time(e1) * 1e3)
         t = torch.tensor(ts, dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        timed.last_min = float(t.min())
+        timed.last_median = float(t.median())
         return float(t.mean())
 
     nominal = rf.Peaks()
     measured = rf.measured_peaks() or rf.Peaks(1642.6, rf.MEASURED_NVLINK_GBS, "measured")
     rows = []
 
-    def record(op, shape, fused_us, base_us, ok, roof_nom, roof_meas):
-        row = {"op": op, "shape": shape, "world": world, "fused_us": round(fused_us, 2), "baseline_us": round(base_us, 2),
+    def record(op, shape, fused_us, base_us, ok, roof_nom, roof_meas, fused_min=None, msg=""):
+        row = {"op": op, "shape": shape, "world": world, "fused_us": round(fused_us, 2),
+               "fused_min_us": round(fused_min, 2) if fused_min is not None else None, "check": msg[:160],
+               "baseline_us": round(base_us, 2),
                "speedup": round(base_us / fused_us, 3), "correct": bool(ok),
                "roofline_nominal_us": round(roof_nom["roofline_us"], 2), "frac_nominal": round(roof_nom["roofline_us"] / fused_us, 3),
                "roofline_measured_us": round(roof_meas["roofline_us"], 2), "frac_measured": round(roof_meas["roofline_us"] / fused_us, 3)}
@@ -103,11 +107,12 @@ def main() -> int:
             data = a2a_ref.generate_input(E, k, H, T, 7, rank, world, dtype="bf16", fixed_tokens=True, weight_mode="softmax",
                                           expert_scale="expert")
             out = a2a_sub.custom_kernel(data)
-            ok, _ = a2a_ref.check_implementation(data, out)
+            ok, msg = a2a_ref.check_implementation(data, out)
             f = timed(lambda: a2a_sub.custom_kernel(data))
+            fmin = timed.last_min
             b = timed(lambda: a2a_base.custom_kernel(data))
             record("a2a", {"tokens": T, "hidden": H, "topk": k, "experts": E}, f, b, ok,
-                   rf.a2a_roofline_us(T, k, H, 2, world, nominal), rf.a2a_roofline_us(T, k, H, 2, world, measured))
+                   rf.a2a_roofline_us(T, k, H, 2, world, nominal), rf.a2a_roofline_us(T, k, H, 2, world, measured), fmin, msg)
         a2a_sub.release_contexts()
     if "gemm_rs" in ops:
         for (m, n, k) in pick("gemm_rs", GEMM_RS_SHAPES):
@@ -115,11 +120,12 @@ def main() -> int:
                 continue
             data = rs_ref.generate_input(rank, world, m, n, k, True, 3, dist="normal")
             out = rs_sub.custom_kernel(data)
-            ok, _ = rs_ref.check_implementation(data, out)
+            ok, msg = rs_ref.check_implementation(data, out)
             f = timed(lambda: rs_sub.custom_kernel(data))
+            fmin = timed.last_min
             b = timed(lambda: rs_base.custom_kernel(data))
             record("gemm_rs", {"m": m, "n": n, "k": k}, f, b, ok, rf.gemm_rs_roofline_us(m, n, k, world, nominal),
-                   rf.gemm_rs_roofline_us(m, n, k, world, measured))
+                   rf.gemm_rs_roofline_us(m, n, k, world, measured), fmin, msg)
         rs_sub.release_contexts()
     if "ag_gemm" in ops:
         for (m, n, k) in pick("ag_gemm", AG_GEMM_SHAPES):
@@ -127,11 +133,12 @@ def main() -> int:
                 continue
             data = ag_ref.generate_input(rank, world, m, n, k, True, 5)
             out = ag_sub.custom_kernel(data)
-            ok, _ = ag_ref.check_implementation(data, out)
+            ok, msg = ag_ref.check_implementation(data, out)
             f = timed(lambda: ag_sub.custom_kernel(data))
+            fmin = timed.last_min
             b = timed(lambda: ag_base.custom_kernel(data))
             record("ag_gemm", {"m": m, "n": n, "k": k}, f, b, ok, rf.ag_gemm_roofline_us(m, n, k, world, nominal),
-                   rf.ag_gemm_roofline_us(m, n, k, world, measured))
+                   rf.ag_gemm_roofline_us(m, n, k, world, measured), fmin, msg)
         ag_sub.release_contexts()
     if rank == 0 and ns.out:
         with open(ns.out, "w") as fh:
