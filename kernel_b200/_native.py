@@ -83,6 +83,7 @@ class A2aArgs(C.Structure):
         ("status", C.c_void_p),
         ("wait_limit_ns", C.c_uint64),
         ("num_ctas", C.c_int),
+        ("trace", C.c_void_p),
     ]
 
 

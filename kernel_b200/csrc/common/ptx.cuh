@@ -135,6 +135,62 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ------------------------------------------------ CTA pairs (cta_group::2) ----
+// Two CTAs of a cluster share one 256-row MMA: each holds its 128 rows of A, its
+// half of B and its 128 accumulator rows; the even CTA (the leader) issues.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Each CTA of the pair loads its own box into its own shared memory; the bytes
+// are counted on the LEADER's mbarrier (`leader_bar` is a cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap, uint32_t leader_bar, int32_t x,
+                                                 int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on ONE mbarrier (given by its cluster address, in either CTA of the
+// pair) once all MMAs issued so far have finished in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+
 // Shared-memory operand descriptor for a K-major bf16 tile stored as rows of
 // 128 bytes (64 elements) with the 128-byte swizzle TMA produces; 8-row groups
 // are 1024 bytes apart.  `addr` is the 1024-byte aligned tile base plus
@@ -172,6 +228,12 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p) {
   return v;
 }
 __device__ __forceinline__ void fence_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+// Plain system-scope store for a flag whose ordering is provided by a
+// fence_sys() the same thread executed just before (fence + relaxed store is a
+// release pattern; st.release would pay for a second fence).
+__device__ __forceinline__ void st_relaxed_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 // 16-byte loads that never use the non-coherent path (data may have been
 // written by a peer GPU during this kernel).
@@ -200,13 +262,20 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
 // Spin on a 32-bit flag until it reaches `want` (flags only grow).  Returns
 // false if `limit_ns` passes first.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint64_t limit_ns) {
-  if (static_cast<int32_t>(ld_acquire_sys_u32(flag) - want) >= 0) return true;
+  // Polls with relaxed loads and pays for one acquire fence once the flag is there.
+  if (static_cast<int32_t>(ld_relaxed_sys_u32(flag) - want) >= 0) {
+    fence_sys();
+    return true;
+  }
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   for (;;) {
-    if (static_cast<int32_t>(ld_acquire_sys_u32(flag) - want) >= 0) return true;
+    if (static_cast<int32_t>(ld_relaxed_sys_u32(flag) - want) >= 0) {
+      fence_sys();
+      return true;
+    }
     if ((++spins & 0xffu) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
-    __nanosleep(32);
+    __nanosleep(20);
   }
 }
 

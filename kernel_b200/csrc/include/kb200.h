@@ -139,6 +139,7 @@ typedef struct KbA2aArgs {
   uint32_t* status;
   uint64_t wait_limit_ns;
   int num_ctas;
+  uint64_t* trace;      // optional device uint64[16]: globaltimer stamps of CTA 0 at the phase boundaries
 } KbA2aArgs;
 
 uint64_t kb_a2a_rows_bytes(int world, int max_tokens, int topk, int hidden, int elem_bytes);

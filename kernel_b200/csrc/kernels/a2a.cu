@@ -51,7 +51,15 @@ struct A2aParams {
   int scale_mode;
   uint32_t* status;
   uint64_t limit_ns;
+  uint64_t* trace;
 };
+
+// Phase stamps (nanoseconds of the global timer) written by thread 0 of CTA 0.
+enum Stamp { ST_ENTRY = 0, ST_SLOTS = 1, ST_PUSHED = 2, ST_DISPATCH_FLAG = 3, ST_EXPERT_GO = 4, ST_COUNTS = 5, ST_EXPERT_ROWS = 6,
+             ST_EXPERT_FLAG = 7, ST_COMBINE_GO = 8, ST_DONE = 9 };
+__device__ __forceinline__ void stamp(const A2aParams& p, int which) {
+  if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[which] = kb::globaltimer_ns();
+}
 
 __device__ __forceinline__ uint8_t* rows_ptr(const A2aParams& p, int on_rank, uint64_t region_off, int src, int slot) {
   return reinterpret_cast<uint8_t*>(p.peer_base[on_rank]) + region_off +
@@ -107,6 +115,7 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh) {
   int32_t* ent_slot = ent_e + MAX_ENT_PER_CTA;
 
   const int tid = threadIdx.x;
+  stamp(p, ST_ENTRY);
   int t0, t1, v0, v1, hs;
   unit_ranges(p, t0, t1, v0, v1, hs);
   const int n_ent = (t1 - t0) * p.k;
@@ -154,6 +163,7 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh) {
     if (hs == 0) p.slots[t0 * p.k + i] = slot;
   }
   __syncthreads();
+  stamp(p, ST_SLOTS);
 
   // Payload: one 16-byte vector per thread, read once, stored k times.
   for (int t = t0; t < t1; ++t) {
@@ -170,6 +180,7 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh) {
       }
     }
   }
+  stamp(p, ST_PUSHED);
   // Per-(source, expert) counts for every destination.
   if (blockIdx.x == 0) {
     for (int e = tid; e < p.E; e += blockDim.x) {
@@ -178,8 +189,9 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh) {
   }
   uint32_t* sync = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.sync_off);
   if (last_block_done(&sync[0], gridDim.x)) {
-    if (tid < p.world) kb::st_release_sys_u32(flag_ptr(p, tid, 0, p.rank), p.epoch);
+    if (tid < p.world) kb::st_release_sys_u32(flag_ptr(p, tid, 0, p.rank), p.epoch);  // threads other than 0 need their own release
   }
+  stamp(p, ST_DISPATCH_FLAG);
 }
 
 __global__ void __launch_bounds__(A2A_THREADS) a2a_dispatch_kernel(const A2aParams p) {
@@ -255,6 +267,7 @@ __device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh) {
     }
   }
   __syncthreads();
+  stamp(p, ST_EXPERT_GO);
   // All counts are fetched in parallel (one independent load per thread), then
   // scanned in shared memory.
   const int32_t* counts = counts_ptr(p, p.rank, 0);
@@ -280,6 +293,7 @@ __device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh) {
     }
   }
   __syncthreads();
+  stamp(p, ST_COUNTS);
   const int total_rows = src_end[p.world - 1];
   for (int g = blockIdx.x; g < total_rows; g += gridDim.x) {
     int s = 0;
@@ -305,10 +319,12 @@ __device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh) {
       dst[v] = Vec16<T>::store(f);
     }
   }
+  stamp(p, ST_EXPERT_ROWS);
   uint32_t* sync = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.sync_off);
   if (last_block_done(&sync[1], gridDim.x)) {
     if (tid < p.world) kb::st_release_sys_u32(flag_ptr(p, tid, 1, p.rank), p.epoch);
   }
+  stamp(p, ST_EXPERT_FLAG);
 }
 
 template <typename T>
@@ -327,6 +343,7 @@ __device__ __forceinline__ void combine_body(const A2aParams& p) {
     }
   }
   __syncthreads();
+  stamp(p, ST_COMBINE_GO);
   int t0, t1, v0, v1, hs;
   unit_ranges(p, t0, t1, v0, v1, hs);
   for (int t = t0; t < t1; ++t) {
@@ -362,6 +379,7 @@ __device__ __forceinline__ void combine_body(const A2aParams& p) {
       reinterpret_cast<uint4*>(p.out + static_cast<size_t>(t) * p.row_bytes)[v] = Vec16<T>::store(acc);
     }
   }
+  stamp(p, ST_DONE);
 }
 
 template <typename T>
@@ -461,6 +479,7 @@ int fill_params(const KbA2aArgs* a, A2aParams* p, int sms) {
   p->scale_mode = a->scale_mode;
   p->status = a->status;
   p->limit_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
+  p->trace = a->trace;
   // Work split: one unit per CTA, about two CTAs per SM.  Units are token
   // groups; with few tokens every group is further split along the hidden
   // dimension so that more SMs take part.

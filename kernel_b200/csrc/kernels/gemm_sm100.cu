@@ -26,6 +26,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "../common/host_util.h"
 #include "../common/ptx.cuh"
@@ -39,23 +41,32 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
-constexpr int GROUP_M = 8;                   // row blocks swept together (rasterisation)
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int B_BYTES = BN * BK * 2;
+// Single CTA: 128x256 tile, B stage = 256 rows, 4 stages of 48 KB.
+// CTA pair (cta_group::2): 256x256 tile over two SMs, each CTA stages its 128
+// rows of A and its 128 of the 256 B rows: 6 stages of 32 KB.
+template <bool kPair>
+struct Cfg {
+  static constexpr int STAGES = kPair ? 6 : 4;
+  static constexpr int B_ROWS = kPair ? 128 : 256;
+  static constexpr int B_BYTES = B_ROWS * BK * 2;
+  static constexpr int GROUP = kPair ? 4 : 8;  // scheduling blocks swept together (1024 rows)
+};
+constexpr int MAX_STAGES = 6;
 constexpr int EPI_COLS = 128;                 // columns staged per epilogue pass
 constexpr int EPI_ROW_BYTES = EPI_COLS * 2;   // 256
 constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;
 constexpr int EPI_BYTES = 4 * EPI_WARP_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int BAR_BYTES = 256;
-constexpr int SMEM_BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + EPI_BYTES + BAR_BYTES;
+constexpr int SMEM_BYTES = 1024 + 4 * (A_BYTES + 32768) + EPI_BYTES + BAR_BYTES;  // same total for both configurations
 constexpr int THREADS_BASE = 256;             // warps 0..3 control, 4..7 epilogue
 constexpr int THREADS_AG = 384;               // + warps 8..11 comm
 
 struct alignas(64) GemmParams {
   CUtensorMap tmA;
   CUtensorMap tmB;
+  CUtensorMap tmOwn;  // AG: this rank's own rows, read in place
   int mode, M, N, K;
   int MB, NB, KB;
   const bf16* bias;
@@ -70,6 +81,11 @@ struct alignas(64) GemmParams {
   uint64_t limit_ns;
   int own_lo_mb, own_hi_mb;
   int ag_parts;
+  // Scheduling blocks: 128 rows (single CTA) or 256 rows (CTA pair).
+  int MBQ, own_lo_q, own_hi_q;
+  int ag_own_direct;  // AG: own row blocks are loaded straight from the input (no self copy)
+  int ag_n_own;  // AG: scheduling blocks per source when they tile the rows evenly, else 0 (plain rotated order)
+  int debug;  // experiments only (KB200_GEMM_DEBUG): 1 no global stores, 2 epilogue only releases TMEM, 4 every load reads tile (0,0), 8 timing words: status[5] max us waited on peers, [6] us until the pushes were out, [7] us until the last epilogue
 };
 
 enum Site : uint32_t {
@@ -93,18 +109,20 @@ struct Smem {
   volatile uint32_t* abort;
 };
 
+template <bool kPair>
 __device__ __forceinline__ Smem carve(uint8_t* raw) {
+  constexpr int STAGES = Cfg<kPair>::STAGES;
   Smem s;
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   s.a = base;
   s.b = base + STAGES * A_BYTES;
-  s.epi = s.b + STAGES * B_BYTES;
+  s.epi = s.b + STAGES * Cfg<kPair>::B_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(s.epi + EPI_BYTES);
   s.full = bars;
-  s.empty = bars + STAGES;
-  s.tfull = bars + 2 * STAGES;
-  s.tempty = bars + 2 * STAGES + 2;
-  s.tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  s.empty = bars + MAX_STAGES;
+  s.tfull = bars + 2 * MAX_STAGES;
+  s.tempty = bars + 2 * MAX_STAGES + 2;
+  s.tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 4);
   s.abort = s.tmem_slot + 1;
   return s;
 }
@@ -120,18 +138,41 @@ __device__ __forceinline__ Smem carve(uint8_t* raw) {
 // the blocks this rank owns form a segment of their own at the very end: a CTA
 // never has a push queued behind one of its own waits, which is what makes
 // the cross-rank waits deadlock-free.
-__device__ __forceinline__ void tile_at(const GemmParams& p, int pos, int& mb, int& nb) {
+template <bool kPair>
+__device__ __forceinline__ void tile_at(const GemmParams& p, int pos, int& mbq, int& nb) {
+  constexpr int GROUP_M = Cfg<kPair>::GROUP;
   int start = 0;
-  int first_len = p.MB;  // blocks in the first segment
+  int first_len = p.MBQ;  // blocks in the first segment
   if (p.mode == KB_GEMM_RS) {
-    start = p.own_hi_mb + 1;
-    first_len = p.MB - (p.own_hi_mb - p.own_lo_mb + 1);
+    start = p.own_hi_q + 1;
+    first_len = p.MBQ - (p.own_hi_q - p.own_lo_q + 1);
   }
-  if (p.mode == KB_GEMM_AG) start = p.own_lo_mb;
+  if (p.mode == KB_GEMM_AG) start = p.own_lo_q;
+  if (p.mode == KB_GEMM_AG && p.ag_n_own > 0) {
+    // Own blocks first, then block c of every other source (nearest first) for
+    // c = 0, 1, ...: the order in which the pushes arrive.  Groups of GROUP_M
+    // consecutive sequence entries are swept column block by column block.
+    const int per_group = GROUP_M * p.NB;
+    const int g = pos / per_group;
+    const int r = pos - g * per_group;
+    int gs = p.MBQ - g * GROUP_M;
+    if (gs > GROUP_M) gs = GROUP_M;
+    nb = r / gs;
+    const int j = g * GROUP_M + (r - nb * gs);
+    if (j < p.ag_n_own) {
+      mbq = p.own_lo_q + j;
+    } else {
+      const int jj = j - p.ag_n_own;
+      const int c = jj / (p.world - 1);
+      const int d = jj - c * (p.world - 1) + 1;
+      mbq = ((p.rank + d) % p.world) * p.ag_n_own + c;
+    }
+    return;
+  }
   int base = 0, blocks = first_len, q = pos;
   if (pos >= first_len * p.NB) {
     base = first_len;
-    blocks = p.MB - first_len;
+    blocks = p.MBQ - first_len;
     q = pos - first_len * p.NB;
   }
   const int per_group = GROUP_M * p.NB;
@@ -141,7 +182,7 @@ __device__ __forceinline__ void tile_at(const GemmParams& p, int pos, int& mb, i
   if (gs > GROUP_M) gs = GROUP_M;
   nb = r / gs;
   const int j = base + g * GROUP_M + (r - nb * gs);
-  mb = (start + j) % p.MB;
+  mbq = (start + j) % p.MBQ;
 }
 
 __device__ __forceinline__ uint32_t* rs_flag(const GemmParams& p, int on_rank, int src, int tile) {
@@ -247,17 +288,26 @@ __device__ __forceinline__ void load_bias8(const bf16* b, float scale, float* ou
   for (int e = 0; e < 8; ++e) out[e] *= scale;
 }
 
-template <int kMode>
+template <int kMode, bool kPair>
 __global__ void __launch_bounds__(kMode == KB_GEMM_AG ? THREADS_AG : THREADS_BASE, 1)
 gemm_kernel(const __grid_constant__ GemmParams p) {
   constexpr bool kAG = (kMode == KB_GEMM_AG);
   constexpr bool kRS = (kMode == KB_GEMM_RS);
+  constexpr int STAGES = Cfg<kPair>::STAGES;
+  constexpr int B_BYTES = Cfg<kPair>::B_BYTES;
+  // In a pair the even CTA leads: it issues the MMAs for both and owns the
+  // barriers the MMA issuer waits on.
+  const uint32_t cta_rank = kPair ? kb::cluster_ctarank() : 0u;
+  const bool leader = (cta_rank == 0u);
+  const int sched_id = kPair ? (blockIdx.x >> 1) : blockIdx.x;
+  const int sched_n = kPair ? (gridDim.x >> 1) : gridDim.x;
   extern __shared__ uint8_t smem_raw[];
-  Smem sm = carve(smem_raw);
+  Smem sm = carve<kPair>(smem_raw);
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int total_tiles = p.MB * p.NB;
+  const int total_tiles = p.MBQ * p.NB;
+  const uint64_t t_start = kb::globaltimer_ns();  // for the optional timing words status[5..7]
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -266,21 +316,28 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     }
     for (int a = 0; a < 2; ++a) {
       kb::mbar_init(&sm.tfull[a], 1);
-      kb::mbar_init(&sm.tempty[a], 4);
+      kb::mbar_init(&sm.tempty[a], kPair ? 8 : 4);  // epilogue warps of both CTAs release the leader's accumulator
     }
     *sm.abort = 0;
     kb::mbar_fence_init();
   }
   if (warp == 2) {
-    kb::tmem_alloc(sm.tmem_slot, TMEM_COLS);
-    kb::tmem_relinquish();
+    if constexpr (kPair) {
+      kb::tmem_alloc_pair(sm.tmem_slot, TMEM_COLS);
+      kb::tmem_relinquish_pair();
+    } else {
+      kb::tmem_alloc(sm.tmem_slot, TMEM_COLS);
+      kb::tmem_relinquish();
+    }
   }
   if (warp == 0 && lane == 0) {
     kb::tma_prefetch_desc(&p.tmA);
     kb::tma_prefetch_desc(&p.tmB);
+    if (kAG && p.ag_own_direct) kb::tma_prefetch_desc(&p.tmOwn);
   }
   kb::tc_fence_before_sync();
   __syncthreads();
+  if constexpr (kPair) kb::cluster_sync_all();  // the partner's barriers exist before anything signals them
   kb::tc_fence_after_sync();
   const uint32_t tmem_base = *sm.tmem_slot;
 
@@ -290,20 +347,27 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       int s = 0;
       uint32_t ph = 0;
       uint64_t ready_mask[4] = {0ull, 0ull, 0ull, 0ull};  // row blocks already seen complete
+      uint64_t waited_ns = 0;
       bool ok = true;
-      for (int pos = blockIdx.x; pos < total_tiles && ok; pos += gridDim.x) {
-        int mb, nb;
-        tile_at(p, pos, mb, nb);
-        if (kAG && !(mb < 256 && ((ready_mask[mb >> 6] >> (mb & 63)) & 1ull))) {
+      for (int pos = sched_id; pos < total_tiles && ok; pos += sched_n) {
+        int mbq, nb;
+        tile_at<kPair>(p, pos, mbq, nb);
+        const int mb = kPair ? 2 * mbq + static_cast<int>(cta_rank) : mbq;
+        const bool own_direct = kAG && p.ag_own_direct && mb >= p.own_lo_mb && mb <= p.own_hi_mb;
+        const CUtensorMap* map_a = own_direct ? &p.tmOwn : &p.tmA;
+        const int a_row = own_direct ? mb * BM - p.rank * p.rpo : mb * BM;
+        if (kAG && !own_direct && mb < p.MB && !(mb < 256 && ((ready_mask[mb >> 6] >> (mb & 63)) & 1ull))) {
           const int s_lo = (mb * BM) / p.rpo;
           int last_row = mb * BM + BM - 1;
           if (last_row > p.M - 1) last_row = p.M - 1;
           const int s_hi = last_row / p.rpo;
+          const uint64_t w0 = kb::globaltimer_ns();
           for (int src = s_lo; src <= s_hi; ++src) {
             if (!kb::wait_flag_ge(ag_flag(p, p.rank, src, mb), p.epoch, p.limit_ns)) {
               kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_AG_FLAG, (uint32_t)src, p.epoch);
             }
           }
+          waited_ns += kb::globaltimer_ns() - w0;
           kb::fence_proxy_async_global();
           if (mb < 256) ready_mask[mb >> 6] |= 1ull << (mb & 63);
         }
@@ -314,26 +378,36 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
             ok = false;
             break;
           }
-          kb::mbar_arrive_expect_tx(&sm.full[s], A_BYTES + B_BYTES);
-          kb::tma_load_2d(sm.a + s * A_BYTES, &p.tmA, &sm.full[s], kb_i * BK, mb * BM);
-          kb::tma_load_2d(sm.b + s * B_BYTES, &p.tmB, &sm.full[s], kb_i * BK, nb * BN);
+          if constexpr (kPair) {
+            // Both CTAs load their own boxes; all bytes are counted on the
+            // leader's barrier, which expects the sum.
+            const uint32_t bar = kb::map_to_cta(kb::smem_u32(&sm.full[s]), 0u);
+            if (leader) kb::mbar_arrive_expect_tx(&sm.full[s], 2 * (A_BYTES + B_BYTES));
+            kb::tma_load_2d_pair(sm.a + s * A_BYTES, map_a, bar, (p.debug & 4) ? 0 : kb_i * BK, (p.debug & 4) ? 0 : a_row);
+            kb::tma_load_2d_pair(sm.b + s * B_BYTES, &p.tmB, bar, (p.debug & 4) ? 0 : kb_i * BK, (p.debug & 4) ? 0 : nb * BN + static_cast<int>(cta_rank) * 128);
+          } else {
+            kb::mbar_arrive_expect_tx(&sm.full[s], A_BYTES + B_BYTES);
+            kb::tma_load_2d(sm.a + s * A_BYTES, map_a, &sm.full[s], (p.debug & 4) ? 0 : kb_i * BK, (p.debug & 4) ? 0 : a_row);
+            kb::tma_load_2d(sm.b + s * B_BYTES, &p.tmB, &sm.full[s], (p.debug & 4) ? 0 : kb_i * BK, (p.debug & 4) ? 0 : nb * BN);
+          }
           if (++s == STAGES) {
             s = 0;
             ph ^= 1u;
           }
         }
       }
+      if (kAG && p.status != nullptr && (p.debug & 8)) atomicMax(&p.status[5], static_cast<uint32_t>(waited_ns / 1000));
     }
     __syncwarp();
   } else if (warp == 1) {
     // -------------------------------------------------------- MMA issuer ----
-    if (lane == 0) {
-      constexpr uint32_t idesc = kb::umma_idesc_bf16(BM, BN);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = kb::umma_idesc_bf16(kPair ? 2 * BM : BM, BN);
       int s = 0;
       uint32_t ph = 0;
       uint32_t it = 0;
       bool ok = true;
-      for (int pos = blockIdx.x; pos < total_tiles && ok; pos += gridDim.x, ++it) {
+      for (int pos = sched_id; pos < total_tiles && ok; pos += sched_n, ++it) {
         const uint32_t acc = it & 1u;
         const uint32_t aph = (it >> 1) & 1u;
         if (!kb::mbar_wait_bounded(&sm.tempty[acc], aph ^ 1u, p.limit_ns)) {
@@ -355,16 +429,36 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           const uint32_t b_addr = kb::smem_u32(sm.b + s * B_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            kb::umma_f16(d, kb::umma_desc_k_sw128(a_addr + k * UMMA_K * 2), kb::umma_desc_k_sw128(b_addr + k * UMMA_K * 2),
-                         idesc, (kb_i | k) != 0 ? 1u : 0u);
+            const uint64_t da = kb::umma_desc_k_sw128(a_addr + k * UMMA_K * 2);
+            const uint64_t db = kb::umma_desc_k_sw128(b_addr + k * UMMA_K * 2);
+            if constexpr (kPair) {
+              kb::umma_f16_pair(d, da, db, idesc, (kb_i | k) != 0 ? 1u : 0u);
+            } else {
+              kb::umma_f16(d, da, db, idesc, (kb_i | k) != 0 ? 1u : 0u);
+            }
           }
-          kb::umma_commit(&sm.empty[s]);
+          if constexpr (kPair) {
+            // The stage is free in both CTAs once these MMAs have read it.
+            const uint32_t e = kb::smem_u32(&sm.empty[s]);
+            kb::umma_commit_pair(kb::map_to_cta(e, 0u));
+            kb::umma_commit_pair(kb::map_to_cta(e, 1u));
+          } else {
+            kb::umma_commit(&sm.empty[s]);
+          }
           if (++s == STAGES) {
             s = 0;
             ph ^= 1u;
           }
         }
-        if (ok) kb::umma_commit(&sm.tfull[acc]);
+        if (ok) {
+          if constexpr (kPair) {
+            const uint32_t f = kb::smem_u32(&sm.tfull[acc]);
+            kb::umma_commit_pair(kb::map_to_cta(f, 0u));
+            kb::umma_commit_pair(kb::map_to_cta(f, 1u));
+          } else {
+            kb::umma_commit(&sm.tfull[acc]);
+          }
+        }
       }
     }
     __syncwarp();
@@ -375,15 +469,28 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     uint8_t* warp_epi = sm.epi + q * EPI_WARP_BYTES;
     constexpr bool rs = kRS;  // the host maps single-rank calls to the plain kernel
     uint32_t it = 0;
-    for (int pos = blockIdx.x; pos < total_tiles; pos += gridDim.x, ++it) {
-      int mb, nb;
-      tile_at(p, pos, mb, nb);
+    uint64_t rs_waited_ns = 0;
+    // Releases this CTA's share of the accumulator: locally for the leader, on
+    // the leader's barrier for its partner.
+    auto release_acc = [&](uint32_t acc) {
+      if constexpr (kPair) {
+        if (leader) kb::mbar_arrive(&sm.tempty[acc]);
+        else kb::mbar_arrive_cluster(kb::map_to_cta(kb::smem_u32(&sm.tempty[acc]), 0u));
+      } else {
+        kb::mbar_arrive(&sm.tempty[acc]);
+      }
+    };
+    for (int pos = sched_id; pos < total_tiles; pos += sched_n, ++it) {
+      int mbq, nb;
+      tile_at<kPair>(p, pos, mbq, nb);
+      const int mb = kPair ? 2 * mbq + static_cast<int>(cta_rank) : mbq;
       const uint32_t acc = it & 1u;
       const uint32_t aph = (it >> 1) & 1u;
-      if (!kb::mbar_wait_bounded(&sm.tfull[acc], aph, p.limit_ns)) {
+      // After a failed wait the loop keeps its shape (the named barriers below
+      // must be reached by all four warps) but stops waiting.
+      if (*sm.abort == 0 && !kb::mbar_wait_bounded(&sm.tfull[acc], aph, p.limit_ns)) {
         kb::report_status(p.status, KB_DEV_TIMEOUT_MBAR, SITE_EPI_TFULL, (uint32_t)pos, p.epoch);
         *sm.abort = 1;
-        break;
       }
       kb::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
@@ -392,7 +499,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       if (last_row > p.M - 1) last_row = p.M - 1;
       int o_lo = 0, o_hi = 0;
       bool has_remote = false, has_own = true;
-      if (rs) {
+      if (rs && row0 < p.M) {
         o_lo = row0 / p.rpo;
         o_hi = last_row / p.rpo;
         has_own = (p.rank >= o_lo && p.rank <= o_hi);
@@ -400,6 +507,12 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       const int tile_id = mb * p.NB + nb;
       bool released = false;
+      if (p.debug & 2) {
+        kb::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) release_acc(acc);
+        continue;
+      }
 
       if (kRS && has_remote) {
         // Phase A: rows that belong to other ranks go to their owners.
@@ -409,7 +522,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           if (h == 1 && !has_own) {
             kb::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) kb::mbar_arrive(&sm.tempty[acc]);
+            if (lane == 0) release_acc(acc);
             released = true;
           }
           __syncwarp();
@@ -442,9 +555,11 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       if (has_own) {
         if (rs) {
           if (et < p.world && et != p.rank) {
+            const uint64_t w0 = kb::globaltimer_ns();
             if (!kb::wait_flag_ge(rs_flag(p, p.rank, et, tile_id), p.epoch, p.limit_ns)) {
               kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_RS_FLAG, (uint32_t)et, p.epoch);
             }
+            rs_waited_ns += kb::globaltimer_ns() - w0;
           }
           epi_bar_sync();
         }
@@ -455,7 +570,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
             if (h == 1) {
               kb::tc_fence_before_sync();
               __syncwarp();
-              if (lane == 0) kb::mbar_arrive(&sm.tempty[acc]);
+              if (lane == 0) release_acc(acc);
               released = true;
             }
             __syncwarp();
@@ -465,7 +580,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
             for (int i = 0; i < 16; ++i) {
               const int row = i * 2 + (lane >> 4);
               const int gr = row0 + q * 32 + row;
-              if (gr < p.M && col < p.N) {
+              if (gr < p.M && col < p.N && !(p.debug & 1)) {
                 const uint4 v = *reinterpret_cast<const uint4*>(warp_epi + row * EPI_ROW_BYTES + ((j ^ (row & 15)) * 16));
                 *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(gr) * p.N + col) = v;
               }
@@ -484,7 +599,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
             if (qd == 3) {
               kb::tc_fence_before_sync();
               __syncwarp();
-              if (lane == 0) kb::mbar_arrive(&sm.tempty[acc]);
+              if (lane == 0) release_acc(acc);
               released = true;
             }
             __syncwarp();
@@ -546,23 +661,29 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       if (!released) {
         kb::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) kb::mbar_arrive(&sm.tempty[acc]);
+        if (lane == 0) release_acc(acc);
       }
+    }
+    if (p.status != nullptr && (p.debug & 8) && lane == 0) {
+      if (kRS) atomicMax(&p.status[5], static_cast<uint32_t>(rs_waited_ns / 1000));
+      atomicMax(&p.status[7], static_cast<uint32_t>((kb::globaltimer_ns() - t_start) / 1000));
     }
   } else if (kAG && warp >= 8) {
     // -------------------------------------------------- all-gather pusher ----
     const int ct = tid - 256;
+    // Every sub-task reads a few of this rank's rows once and stores them into
+    // the gather buffer of every rank (self included); sub-tasks run row block
+    // by row block, so that all destinations receive block c at about the same
+    // time, which is the order in which their GEMMs consume it.  The last
+    // sub-task of a row block releases that block's flag on every rank.
     const int n_chunks = p.own_hi_mb - p.own_lo_mb + 1;
     const int parts = p.ag_parts;
-    const int total_tasks = p.world * n_chunks * parts;
+    const int total_tasks = n_chunks * parts;
     const int own_row0 = p.rank * p.rpo;
     uint32_t* counters = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.counter_off);
     for (int t = blockIdx.x; t < total_tasks; t += gridDim.x) {
-      const int dj = t / (n_chunks * parts);
-      const int rem = t - dj * (n_chunks * parts);
-      const int c = rem / parts;
-      const int part = rem - c * parts;
-      const int dst = (p.rank - dj + p.world) % p.world;
+      const int c = t / parts;
+      const int part = t - c * parts;
       const int mb = p.own_lo_mb + c;
       int r_begin = mb * BM;
       if (r_begin < own_row0) r_begin = own_row0;
@@ -571,43 +692,58 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       if (r_end > p.M) r_end = p.M;
       const int rows = r_end - r_begin;
       const int per = (rows + parts - 1) / parts;
-      int rb = r_begin + part * per;
+      const int rb = r_begin + part * per;
       int re = rb + per;
       if (re > r_end) re = r_end;
       if (rb < re) {
         const size_t nvec = static_cast<size_t>(re - rb) * p.K / 8;
         const uint4* src = reinterpret_cast<const uint4*>(p.a_local + static_cast<size_t>(rb - own_row0) * p.K);
-        uint4* dstp = reinterpret_cast<uint4*>(ag_gather_row(p, dst, rb));
+        const int dd0 = p.ag_own_direct ? 1 : 0;  // the GEMM reads own rows in place
         size_t v = ct;
-        for (; v + 3 * 128 < nvec; v += 4 * 128) {
-          const uint4 x0 = kb::ld_nc_v4(src + v);
-          const uint4 x1 = kb::ld_nc_v4(src + v + 128);
-          const uint4 x2 = kb::ld_nc_v4(src + v + 256);
-          const uint4 x3 = kb::ld_nc_v4(src + v + 384);
-          kb::st_sys_v4(dstp + v, x0);
-          kb::st_sys_v4(dstp + v + 128, x1);
-          kb::st_sys_v4(dstp + v + 256, x2);
-          kb::st_sys_v4(dstp + v + 384, x3);
+        for (; v + 7 * 128 < nvec; v += 8 * 128) {
+          uint4 x[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) x[u] = kb::ld_nc_v4(src + v + u * 128);
+          for (int dd = dd0; dd < p.world; ++dd) {
+            const int dst = (p.rank - dd + p.world) % p.world;
+            uint4* dstp = reinterpret_cast<uint4*>(ag_gather_row(p, dst, rb));
+#pragma unroll
+            for (int u = 0; u < 8; ++u) kb::st_sys_v4(dstp + v + u * 128, x[u]);
+          }
         }
-        for (; v < nvec; v += 128) kb::st_sys_v4(dstp + v, kb::ld_nc_v4(src + v));
+        for (; v < nvec; v += 128) {
+          const uint4 x0 = kb::ld_nc_v4(src + v);
+          for (int dd = dd0; dd < p.world; ++dd) {
+            const int dst = (p.rank - dd + p.world) % p.world;
+            kb::st_sys_v4(reinterpret_cast<uint4*>(ag_gather_row(p, dst, rb)) + v, x0);
+          }
+        }
       }
       comm_bar_sync();
       if (ct == 0) {
         kb::fence_sys();
-        const uint32_t old = atomicAdd(&counters[dst * n_chunks + c], 1u);
+        const uint32_t old = atomicAdd(&counters[c], 1u);
         if ((old + 1u) % static_cast<uint32_t>(parts) == 0u) {
           kb::fence_sys();
-          kb::st_release_sys_u32(ag_flag(p, dst, p.rank, mb), p.epoch);
+          for (int dd = p.ag_own_direct ? 1 : 0; dd < p.world; ++dd) {
+            const int dst = (p.rank - dd + p.world) % p.world;
+            kb::st_relaxed_sys_u32(ag_flag(p, dst, p.rank, mb), p.epoch);
+          }
         }
       }
+    }
+    if (ct == 0 && p.status != nullptr && (p.debug & 8)) {
+      atomicMax(&p.status[6], static_cast<uint32_t>((kb::globaltimer_ns() - t_start) / 1000));
     }
   }
 
   kb::tc_fence_before_sync();
   __syncthreads();
+  if constexpr (kPair) kb::cluster_sync_all();  // nobody leaves while the partner may still signal or read
   if (warp == 2) {
     kb::tc_fence_after_sync();
-    kb::tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (kPair) kb::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else kb::tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -631,6 +767,11 @@ int make_tmap(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, u
 }
 
 inline uint64_t round_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+inline bool getenv_flag(const char* name) {
+  const char* v = getenv(name);
+  return v != nullptr && v[0] == '1';
+}
 
 }  // namespace
 
@@ -686,7 +827,7 @@ extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {
   p.data_off = a->data_off;
   p.flag_off = a->flag_off;
   p.counter_off = a->counter_off;
-  p.ag_parts = 8;
+  p.ag_parts = 32;
   for (int r = 0; r < a->world; ++r) p.peer_base[r] = static_cast<char*>(a->peer_base[r]);
 
   const void* a_ptr = a->A;
@@ -728,30 +869,73 @@ extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {
     }
   }
 
-  int rc = make_tmap(&p.tmA, a_ptr, a_rows, a->K, BM);
-  if (rc != KB_OK) return rc;
-  rc = make_tmap(&p.tmB, a->B, a->N, a->K, BN);
-  if (rc != KB_OK) return rc;
+  // CTA pairs need 256-row scheduling blocks that do not straddle two ranks.
+  // num_ctas bit 30 forces the single-CTA kernel (tests, comparisons).
+  {
+    const char* dbg = getenv("KB200_GEMM_DEBUG");
+    p.debug = dbg ? atoi(dbg) : 0;
+  }
+  const bool forbid_pair = (a->num_ctas & (1 << 30)) != 0 || getenv_flag("KB200_GEMM_NO_PAIR");
+  const int req_ctas = a->num_ctas & ~(1 << 30);
+  const bool dist_mode = (p.mode != KB_GEMM_PLAIN);
+  bool pair = !forbid_pair && a->M >= 256 && (!dist_mode || (p.rpo % 256) == 0);
 
   int dev = 0, sms = 0;
   KB_CUDA_OK(cudaGetDevice(&dev));
   KB_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const int total_tiles = p.MB * p.NB;
-  int grid = a->num_ctas > 0 ? a->num_ctas : sms;
+  int grid = req_ctas > 0 ? req_ctas : sms;
   if (grid > sms) grid = sms;
-  const bool ag = (p.mode == KB_GEMM_AG);
-  if (!ag && grid > total_tiles) grid = total_tiles;
-
-  if (p.mode == KB_GEMM_AG) {
-    KB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<KB_GEMM_AG>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    gemm_kernel<KB_GEMM_AG><<<grid, THREADS_AG, SMEM_BYTES, stream>>>(p);
-  } else if (p.mode == KB_GEMM_RS) {
-    KB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<KB_GEMM_RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    gemm_kernel<KB_GEMM_RS><<<grid, THREADS_BASE, SMEM_BYTES, stream>>>(p);
-  } else {
-    KB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<KB_GEMM_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    gemm_kernel<KB_GEMM_PLAIN><<<grid, THREADS_BASE, SMEM_BYTES, stream>>>(p);
+  if (pair) {
+    grid &= ~1;
+    if (grid < 2) pair = false;
   }
+  const int block_rows = pair ? 256 : 128;
+  p.MBQ = (a->M + block_rows - 1) / block_rows;
+  p.own_lo_q = dist_mode ? (a->rank * p.rpo) / block_rows : 0;
+  p.own_hi_q = dist_mode ? ((a->rank + 1) * p.rpo - 1) / block_rows : p.MBQ - 1;
+  p.ag_n_own = (p.mode == KB_GEMM_AG && (p.rpo % block_rows) == 0) ? p.rpo / block_rows : 0;
+
+  int rc = make_tmap(&p.tmA, a_ptr, a_rows, a->K, BM);
+  if (rc != KB_OK) return rc;
+  rc = make_tmap(&p.tmB, a->B, a->N, a->K, pair ? 128 : BN);
+  if (rc != KB_OK) return rc;
+  p.ag_own_direct = 0;
+  if (p.mode == KB_GEMM_AG && (p.rpo % BM) == 0) {
+    rc = make_tmap(&p.tmOwn, a->A, p.rpo, a->K, BM);
+    if (rc != KB_OK) return rc;
+    p.ag_own_direct = 1;
+  }
+
+  const int total_units = p.MBQ * p.NB * (pair ? 2 : 1);
+  const bool ag = (p.mode == KB_GEMM_AG);
+  if (!ag && grid > total_units) grid = total_units;
+
+  const int threads = ag ? THREADS_AG : THREADS_BASE;
+  const void* fn = nullptr;
+  if (pair) {
+    fn = ag ? (const void*)gemm_kernel<KB_GEMM_AG, true>
+            : (p.mode == KB_GEMM_RS ? (const void*)gemm_kernel<KB_GEMM_RS, true> : (const void*)gemm_kernel<KB_GEMM_PLAIN, true>);
+  } else {
+    fn = ag ? (const void*)gemm_kernel<KB_GEMM_AG, false>
+            : (p.mode == KB_GEMM_RS ? (const void*)gemm_kernel<KB_GEMM_RS, false> : (const void*)gemm_kernel<KB_GEMM_PLAIN, false>);
+  }
+  KB_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pair) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  void* args[] = {&p};
+  KB_CUDA_OK(cudaLaunchKernelExC(&cfg, fn, args));
   KB_CUDA_OK(cudaGetLastError());
   return KB_OK;
 }

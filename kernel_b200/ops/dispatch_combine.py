@@ -75,6 +75,9 @@ class MoEAllToAll:
             self.status = self.heap.status
             self._eb = eb
             self._fused = os.environ.get("KB200_A2A_FUSED", "1") == "1"
+            self._trace = None
+            if os.environ.get("KB200_TRACE", "0") == "1":
+                self.enable_trace()
 
     # ------------------------------------------------------------- native ----
     def _args(self, x, indices, weights, out, scale_mode) -> N.A2aArgs:
@@ -94,7 +97,26 @@ class MoEAllToAll:
         a.scale_mode = scale_mode
         a.status = self.status.data_ptr()
         a.wait_limit_ns = _WAIT_LIMIT_NS
+        a.trace = self._trace.data_ptr() if self._trace is not None else None
         return a
+
+    # -------------------------------------------------------------- tracing ----
+    TRACE_PHASES = ("slots", "push", "dispatch_flag", "wait_dispatch", "counts", "expert_rows", "expert_flag",
+                    "wait_expert", "combine")
+
+    def enable_trace(self, on: bool = True) -> None:
+        """Phase stamps: CTA 0 records the global timer at every phase boundary of
+        the next calls (the role of the reference's per-phase ``TimingContext``,
+        ``all2all/submission_timed.py:9-33``, without host synchronisation)."""
+        self._trace = torch.zeros(16, dtype=torch.int64, device=self.heap.device) if on else None
+
+    def read_trace(self) -> dict:
+        """Durations in microseconds between consecutive stamps of the last call
+        (synchronises).  ``total`` is entry to end as seen by CTA 0."""
+        t = self._trace.cpu().tolist()
+        out = {name: (t[i + 1] - t[i]) / 1e3 for i, name in enumerate(self.TRACE_PHASES)}
+        out["total"] = (t[9] - t[0]) / 1e3
+        return out
 
     def _validate(self, x, indices, weights) -> None:
         T = x.shape[0]

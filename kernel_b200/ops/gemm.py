@@ -39,8 +39,11 @@ def _launch(args: N.GemmArgs, device: torch.device) -> None:
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-         bias_scale: float = 1.0, status: Optional[torch.Tensor] = None, num_ctas: int = 0) -> torch.Tensor:
-    """``out[M,N] = a[M,K] @ b[N,K]^T (+ bias_scale * bias)`` in bf16 with fp32 accumulation."""
+         bias_scale: float = 1.0, status: Optional[torch.Tensor] = None, num_ctas: int = 0, pair: bool = True) -> torch.Tensor:
+    """``out[M,N] = a[M,K] @ b[N,K]^T (+ bias_scale * bias)`` in bf16 with fp32 accumulation.
+
+    ``pair=False`` forces the single-CTA 128x256 kernel; by default two CTAs of a
+    cluster share 256x256 tiles (``cta_group::2``) when M >= 256."""
     _check_bf16_2d(a, "a")
     _check_bf16_2d(b, "b")
     M, K = a.shape
@@ -67,7 +70,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, 
     args.rank, args.world, args.epoch = 0, 1, 1
     args.status = status.data_ptr() if status is not None else None
     args.wait_limit_ns = _WAIT_LIMIT_NS
-    args.num_ctas = num_ctas
+    args.num_ctas = num_ctas | (0 if pair else (1 << 30))
     _launch(args, a.device)
     return out
 

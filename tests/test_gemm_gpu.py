@@ -6,6 +6,8 @@ pytestmark = pytest.mark.gpu
 
 SHAPES = [
     (128, 256, 64),      # one tile, one k-block
+    (256, 256, 64),      # one pair tile
+    (384, 512, 192),     # odd number of 128-row blocks: the partner CTA of the last pair is all padding
     (128, 256, 256),     # one tile, ring wraps once
     (256, 512, 512),     # 2x2 tiles
     (128, 256, 48),      # K tail inside the first block
@@ -26,7 +28,8 @@ def _ref(a, b, bias, scale):
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
 @pytest.mark.parametrize("has_bias", [False, True])
-def test_gemm_matches_fp32_reference(M, N, K, has_bias):
+@pytest.mark.parametrize("pair", [True, False])
+def test_gemm_matches_fp32_reference(M, N, K, has_bias, pair):
     from kernel_b200.ops.gemm import gemm
 
     torch.manual_seed(M * 7 + N * 3 + K)
@@ -35,7 +38,7 @@ def test_gemm_matches_fp32_reference(M, N, K, has_bias):
     b = (torch.randn(N, K, device=dev) / K ** 0.5).to(torch.bfloat16)
     bias = (torch.randn(N, device=dev) * 0.02).to(torch.bfloat16) if has_bias else None
     status = torch.zeros(8, dtype=torch.int32, device=dev)
-    out = gemm(a, b, bias, bias_scale=2.0 if has_bias else 1.0, status=status)
+    out = gemm(a, b, bias, bias_scale=2.0 if has_bias else 1.0, status=status, pair=pair)
     torch.cuda.synchronize()
     assert status.cpu().tolist()[0] == 0, f"device status {status.cpu().tolist()}"
     ref = _ref(a, b, bias, 2.0)
@@ -62,7 +65,8 @@ def test_gemm_few_ctas_exercises_persistent_loop():
     dev = torch.device("cuda")
     a = torch.randn(1024, 512, device=dev).to(torch.bfloat16)
     b = (torch.randn(1024, 512, device=dev) / 512 ** 0.5).to(torch.bfloat16)
-    out = gemm(a, b, num_ctas=3)  # 32 tiles on 3 CTAs: both accumulators, many ring wraps
     ref = _ref(a, b, None, 1.0)
-    torch.cuda.synchronize()
-    assert torch.allclose(out.float(), ref, rtol=1e-2, atol=1e-2)
+    for pair, ctas in ((False, 3), (True, 2), (True, 6)):  # few CTAs: both accumulators, many ring wraps
+        out = gemm(a, b, num_ctas=ctas, pair=pair)
+        torch.cuda.synchronize()
+        assert torch.allclose(out.float(), ref, rtol=1e-2, atol=1e-2), (pair, ctas)
