@@ -262,20 +262,25 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
 // Spin on a 32-bit flag until it reaches `want` (flags only grow).  Returns
 // false if `limit_ns` passes first.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint64_t limit_ns) {
-  // Polls with relaxed loads and pays for one acquire fence once the flag is there.
+  // Polls with relaxed loads and pays for one acquire fence once the flag is
+  // there.  The pause between polls doubles up to half a microsecond: hundreds
+  // of CTAs poll words of the same cache line, and an unthrottled spin takes
+  // L2 bandwidth away from the very stores it is waiting for.
   if (static_cast<int32_t>(ld_relaxed_sys_u32(flag) - want) >= 0) {
     fence_sys();
     return true;
   }
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
+  uint32_t pause = 32;
   for (;;) {
+    __nanosleep(pause);
+    if (pause < 512) pause *= 2;
     if (static_cast<int32_t>(ld_relaxed_sys_u32(flag) - want) >= 0) {
       fence_sys();
       return true;
     }
-    if ((++spins & 0xffu) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
-    __nanosleep(20);
+    if ((++spins & 0x3fu) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
   }
 }
 

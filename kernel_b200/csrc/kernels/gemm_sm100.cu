@@ -671,63 +671,68 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
   } else if (kAG && warp >= 8) {
     // -------------------------------------------------- all-gather pusher ----
     const int ct = tid - 256;
-    // Every sub-task reads a few of this rank's rows once and stores them into
-    // the gather buffer of every rank (self included); sub-tasks run row block
-    // by row block, so that all destinations receive block c at about the same
-    // time, which is the order in which their GEMMs consume it.  The last
-    // sub-task of a row block releases that block's flag on every rank.
+    // Row block by row block, all CTAs together: each takes an equal slice of the
+    // block's bytes (rows are contiguous in the input and in the gather buffers),
+    // reads it once and stores it into the gather buffer of every other rank
+    // (and of this rank, unless the GEMM reads its own rows in place).  Blocks
+    // therefore arrive everywhere in ascending order, which is the order in
+    // which the GEMMs consume them.  The last CTA to finish its slice of a block
+    // releases the block's flag on every rank.
     const int n_chunks = p.own_hi_mb - p.own_lo_mb + 1;
-    const int parts = p.ag_parts;
-    const int total_tasks = n_chunks * parts;
     const int own_row0 = p.rank * p.rpo;
+    const int dd0 = p.ag_own_direct ? 1 : 0;
     uint32_t* counters = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.counter_off);
-    for (int t = blockIdx.x; t < total_tasks; t += gridDim.x) {
-      const int c = t / parts;
-      const int part = t - c * parts;
+    // Completion (CTA barrier, system fence, counter) is paid once per group of
+    // row blocks, at most eight times per call.
+    const int group = (n_chunks + 7) / 8;
+    for (int c = 0; c < n_chunks; ++c) {
       const int mb = p.own_lo_mb + c;
       int r_begin = mb * BM;
       if (r_begin < own_row0) r_begin = own_row0;
       int r_end = mb * BM + BM;
       if (r_end > own_row0 + p.rpo) r_end = own_row0 + p.rpo;
       if (r_end > p.M) r_end = p.M;
-      const int rows = r_end - r_begin;
-      const int per = (rows + parts - 1) / parts;
-      const int rb = r_begin + part * per;
-      int re = rb + per;
-      if (re > r_end) re = r_end;
-      if (rb < re) {
-        const size_t nvec = static_cast<size_t>(re - rb) * p.K / 8;
-        const uint4* src = reinterpret_cast<const uint4*>(p.a_local + static_cast<size_t>(rb - own_row0) * p.K);
-        const int dd0 = p.ag_own_direct ? 1 : 0;  // the GEMM reads own rows in place
-        size_t v = ct;
-        for (; v + 7 * 128 < nvec; v += 8 * 128) {
-          uint4 x[8];
+      const size_t nvec = static_cast<size_t>(r_end - r_begin) * p.K / 8;
+      size_t per = (nvec + gridDim.x - 1) / gridDim.x;
+      per = (per + 127) / 128 * 128;
+      size_t lo = static_cast<size_t>(blockIdx.x) * per;
+      size_t hi = lo + per;
+      if (lo > nvec) lo = nvec;
+      if (hi > nvec) hi = nvec;
+      const uint4* src = reinterpret_cast<const uint4*>(p.a_local + static_cast<size_t>(r_begin - own_row0) * p.K);
+      // Up to eight independent 16-byte loads per thread are in flight before the
+      // first store, whatever the length of the slice.
+      for (size_t base = lo; base < hi; base += 8 * 128) {
+        uint4 x[8];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) x[u] = kb::ld_nc_v4(src + v + u * 128);
-          for (int dd = dd0; dd < p.world; ++dd) {
-            const int dst = (p.rank - dd + p.world) % p.world;
-            uint4* dstp = reinterpret_cast<uint4*>(ag_gather_row(p, dst, rb));
-#pragma unroll
-            for (int u = 0; u < 8; ++u) kb::st_sys_v4(dstp + v + u * 128, x[u]);
-          }
+        for (int u = 0; u < 8; ++u) {
+          const size_t v = base + u * 128 + ct;
+          if (v < hi) x[u] = kb::ld_nc_v4(src + v);
         }
-        for (; v < nvec; v += 128) {
-          const uint4 x0 = kb::ld_nc_v4(src + v);
-          for (int dd = dd0; dd < p.world; ++dd) {
-            const int dst = (p.rank - dd + p.world) % p.world;
-            kb::st_sys_v4(reinterpret_cast<uint4*>(ag_gather_row(p, dst, rb)) + v, x0);
+        for (int dd = dd0; dd < p.world; ++dd) {
+          const int dst = (p.rank - dd + p.world) % p.world;
+          uint4* dstp = reinterpret_cast<uint4*>(ag_gather_row(p, dst, r_begin));
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const size_t v = base + u * 128 + ct;
+            if (v < hi) kb::st_sys_v4(dstp + v, x[u]);
           }
         }
       }
+      const bool group_end = ((c + 1) % group == 0) || (c + 1 == n_chunks);
+      if (!group_end) continue;
       comm_bar_sync();
       if (ct == 0) {
         kb::fence_sys();
-        const uint32_t old = atomicAdd(&counters[c], 1u);
-        if ((old + 1u) % static_cast<uint32_t>(parts) == 0u) {
+        const int g = c / group;
+        const uint32_t old = atomicAdd(&counters[g], 1u);
+        if ((old + 1u) % gridDim.x == 0u) {
           kb::fence_sys();
-          for (int dd = p.ag_own_direct ? 1 : 0; dd < p.world; ++dd) {
-            const int dst = (p.rank - dd + p.world) % p.world;
-            kb::st_relaxed_sys_u32(ag_flag(p, dst, p.rank, mb), p.epoch);
+          for (int cc = g * group; cc <= c; ++cc) {
+            for (int dd = dd0; dd < p.world; ++dd) {
+              const int dst = (p.rank - dd + p.world) % p.world;
+              kb::st_relaxed_sys_u32(ag_flag(p, dst, p.rank, p.own_lo_mb + cc), p.epoch);
+            }
           }
         }
       }
@@ -874,6 +879,7 @@ extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {
   {
     const char* dbg = getenv("KB200_GEMM_DEBUG");
     p.debug = dbg ? atoi(dbg) : 0;
+
   }
   const bool forbid_pair = (a->num_ctas & (1 << 30)) != 0 || getenv_flag("KB200_GEMM_NO_PAIR");
   const int req_ctas = a->num_ctas & ~(1 << 30);
