@@ -578,8 +578,16 @@ static int launch_fused(const A2aParams& p, int sms, cudaStream_t st) {
   const size_t smem_d = (3 * p.E + 2 * MAX_ENT_PER_CTA) * sizeof(int32_t);
   const size_t smem_e = (p.world * p.El + p.world) * sizeof(int32_t);
   const size_t smem = smem_d > smem_e ? smem_d : smem_e;
-  int per_sm = 0;
-  KB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, a2a_fused_kernel<T>, A2A_THREADS, smem));
+  // The occupancy query costs microseconds of host time; its answer depends only
+  // on the kernel instance and the shared-memory size.
+  static size_t cached_smem = ~size_t(0);
+  static int cached_per_sm = 0;
+  int per_sm = cached_per_sm;
+  if (cached_smem != smem) {
+    KB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, a2a_fused_kernel<T>, A2A_THREADS, smem));
+    cached_smem = smem;
+    cached_per_sm = per_sm;
+  }
   const int units = p.tok_groups * p.h_splits;
   if (per_sm < 1 || units > per_sm * sms) {
     kb::set_error("a2a fused: %d CTAs cannot be co-resident (%d per SM)", units, per_sm);

@@ -76,6 +76,8 @@ class MoEAllToAll:
             self._eb = eb
             self._fused = os.environ.get("KB200_A2A_FUSED", "1") == "1"
             self._trace = None
+            self._hot_args = None
+            self._lib = lib
             if os.environ.get("KB200_TRACE", "0") == "1":
                 self.enable_trace()
 
@@ -138,20 +140,32 @@ class MoEAllToAll:
         global launch_count
         out = torch.empty_like(x)
         self.epoch += 1
-        a = self._args(x, indices, weights, out, scale_mode)
-        lib = N.lib()
-        st = torch.cuda.current_stream(x.device).cuda_stream
+        # The argument block is built once; a call only refreshes what changes.
+        # Host time matters here: a rank whose launch is late keeps all its peers
+        # waiting inside their kernels.
+        a = self._hot_args
+        if a is None:
+            a = self._hot_args = self._args(x, indices, weights, out, scale_mode)
+            self._hot_ref = C.byref(a)
+            self._stream_of = torch.cuda.current_stream
+        else:
+            a.num_tokens = x.shape[0]
+            a.x, a.indices, a.weights, a.out = x.data_ptr(), indices.data_ptr(), weights.data_ptr(), out.data_ptr()
+            a.epoch, a.scale_mode = self.epoch, scale_mode
+            a.trace = self._trace.data_ptr() if self._trace is not None else None
+        st = self._stream_of(x.device).cuda_stream
+        lib = self._lib
         if self._fused:
-            code = lib.kb_a2a_round_trip(C.byref(a), st)
+            code = lib.kb_a2a_round_trip(self._hot_ref, st)
             if code == N.KB_OK:
                 launch_count += 1
                 return out
             if code != N.KB_ERR_UNSUPPORTED:
                 N.check(code)
             self._fused = False  # too many CTAs for one cooperative launch: three launches
-        N.check(lib.kb_a2a_dispatch(C.byref(a), st))
-        N.check(lib.kb_a2a_expert_scale(C.byref(a), st))
-        N.check(lib.kb_a2a_combine(C.byref(a), st))
+        N.check(lib.kb_a2a_dispatch(self._hot_ref, st))
+        N.check(lib.kb_a2a_expert_scale(self._hot_ref, st))
+        N.check(lib.kb_a2a_combine(self._hot_ref, st))
         launch_count += 3
         return out
 

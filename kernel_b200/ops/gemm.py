@@ -34,7 +34,9 @@ def _check_bf16_2d(t: torch.Tensor, name: str) -> None:
 def _launch(args: N.GemmArgs, device: torch.device) -> None:
     global launch_count
     stream = torch.cuda.current_stream(device).cuda_stream
-    N.check(N.lib().kb_gemm(C.byref(args), stream))
+    code = N.lib().kb_gemm(C.byref(args), stream)
+    if code:
+        N.check(code)
     launch_count += 1
 
 
@@ -94,6 +96,7 @@ class GemmRS:
         self.native = torch.cuda.is_available() and (device is None or torch.device(device).type == "cuda")
         self.epoch = 0
         self.heap = None
+        self._hot = None
         if self.native and self.world > 1:
             lib = N.lib()
             data = int(lib.kb_gemm_rs_data_bytes(M, Nn, self.world))
@@ -130,18 +133,22 @@ class GemmRS:
         if out is None:
             out = torch.empty((rows, self.N), dtype=torch.bfloat16, device=a.device)
         self.epoch += 1
-        args = N.GemmArgs()
-        args.mode = N.GEMM_RS
-        args.M, args.N, args.K = M, self.N, K
+        args = self._hot
+        if args is None:  # built once; calls only refresh pointers, K and the epoch
+            args = self._hot = N.GemmArgs()
+            args.mode = N.GEMM_RS
+            args.M, args.N = M, self.N
+            args.rank, args.world = self.rank, self.world
+            if self.heap is not None:
+                args.peer_base = self.heap.peer_array()
+                args.data_off, args.flag_off = self.data_off, self.flag_off
+            args.status = self.status.data_ptr()
+            args.wait_limit_ns = _WAIT_LIMIT_NS
+        args.K = K
         args.A, args.B, args.out = a.data_ptr(), w.data_ptr(), out.data_ptr()
         args.bias = bias.data_ptr() if bias is not None else None
         args.bias_scale = bias_scale
-        args.rank, args.world, args.epoch = self.rank, self.world, self.epoch
-        if self.heap is not None:
-            args.peer_base = self.heap.peer_array()
-            args.data_off, args.flag_off = self.data_off, self.flag_off
-        args.status = self.status.data_ptr()
-        args.wait_limit_ns = _WAIT_LIMIT_NS
+        args.epoch = self.epoch
         _launch(args, a.device)
         return out
 
@@ -162,6 +169,7 @@ class AGGemm:
         self.native = torch.cuda.is_available() and (device is None or torch.device(device).type == "cuda")
         self.epoch = 0
         self.heap = None
+        self._hot = None
         if self.native and self.world > 1:
             lib = N.lib()
             data = int(lib.kb_gemm_ag_data_bytes(M, K))
@@ -200,17 +208,21 @@ class AGGemm:
         if out is None:
             out = torch.empty((self.M, Nl), dtype=torch.bfloat16, device=a_local.device)
         self.epoch += 1
-        args = N.GemmArgs()
-        args.mode = N.GEMM_AG
-        args.M, args.N, args.K = self.M, Nl, K
+        args = self._hot
+        if args is None:
+            args = self._hot = N.GemmArgs()
+            args.mode = N.GEMM_AG
+            args.M, args.K = self.M, K
+            args.bias_scale = 1.0
+            args.rank, args.world = self.rank, self.world
+            if self.heap is not None:
+                args.peer_base = self.heap.peer_array()
+                args.data_off, args.flag_off, args.counter_off = self.data_off, self.flag_off, self.counter_off
+            args.status = self.status.data_ptr()
+            args.wait_limit_ns = _WAIT_LIMIT_NS
+        args.N = Nl
         args.A, args.B, args.out = a_local.data_ptr(), w.data_ptr(), out.data_ptr()
         args.bias = bias.data_ptr() if bias is not None else None
-        args.bias_scale = 1.0
-        args.rank, args.world, args.epoch = self.rank, self.world, self.epoch
-        if self.heap is not None:
-            args.peer_base = self.heap.peer_array()
-            args.data_off, args.flag_off, args.counter_off = self.data_off, self.flag_off, self.counter_off
-        args.status = self.status.data_ptr()
-        args.wait_limit_ns = _WAIT_LIMIT_NS
+        args.epoch = self.epoch
         _launch(args, a_local.device)
         return out

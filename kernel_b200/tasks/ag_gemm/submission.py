@@ -17,7 +17,7 @@ def _group_key():
 
 
 def get_context(M: int, K: int, device: torch.device) -> AGGemm:
-    key = (M, K, str(device), _group_key())
+    key = (M, K, device.type, device.index, _group_key())
     ctx = _contexts.get(key)
     if ctx is None:
         ctx = AGGemm(M, K, device=device)

@@ -23,7 +23,7 @@ def _group_key():
 
 def get_context(cfg, world_size: int, device: torch.device) -> MoEAllToAll:
     key = (cfg.num_experts, cfg.experts_per_token, cfg.hidden_dim, cfg.max_num_tokens, cfg.in_dtype, world_size,
-           str(device), _group_key())
+           device.type, device.index, _group_key())
     ctx = _contexts.get(key)
     if ctx is None:
         ctx = MoEAllToAll(cfg.num_experts, cfg.experts_per_token, cfg.hidden_dim, cfg.max_num_tokens,

@@ -20,7 +20,7 @@ def _group_key():
 
 
 def get_context(M: int, N: int, device: torch.device) -> GemmRS:
-    key = (M, N, str(device), _group_key())
+    key = (M, N, device.type, device.index, _group_key())
     ctx = _contexts.get(key)
     if ctx is None:
         ctx = GemmRS(M, N, device=device)
