@@ -41,8 +41,13 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--timing-words", action="store_true",
+                    help="GEMM ops: also report the kernel's timing words (us waited on peers, us until pushes were out, "
+                         "us until the last epilogue; maximum over CTAs, calls and ranks)")
     ns = ap.parse_args()
 
+    if ns.timing_words:
+        os.environ["KB200_GEMM_DEBUG"] = "8"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -87,13 +92,23 @@ def main() -> int:
     measured = rf.measured_peaks() or rf.Peaks(1642.6, rf.MEASURED_NVLINK_GBS, "measured")
     rows = []
 
-    def record(op, shape, fused_us, base_us, ok, roof_nom, roof_meas, fused_min=None, msg=""):
+    def timing_words(ctx):
+        if not ns.timing_words or ctx is None:
+            return None
+        w = ctx.status[5:8].to(torch.int64).clone()
+        dist.all_reduce(w, op=dist.ReduceOp.MAX)
+        ctx.status.zero_()
+        return w.tolist()
+
+    def record(op, shape, fused_us, base_us, ok, roof_nom, roof_meas, fused_min=None, msg="", words=None):
         row = {"op": op, "shape": shape, "world": world, "fused_us": round(fused_us, 2),
                "fused_min_us": round(fused_min, 2) if fused_min is not None else None, "check": msg[:160],
                "baseline_us": round(base_us, 2),
                "speedup": round(base_us / fused_us, 3), "correct": bool(ok),
                "roofline_nominal_us": round(roof_nom["roofline_us"], 2), "frac_nominal": round(roof_nom["roofline_us"] / fused_us, 3),
                "roofline_measured_us": round(roof_meas["roofline_us"], 2), "frac_measured": round(roof_meas["roofline_us"] / fused_us, 3)}
+        if words is not None:
+            row["timing_words_us"] = {"waited_on_peers": words[0], "pushes_out": words[1], "last_epilogue": words[2]}
         rows.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)
@@ -121,11 +136,14 @@ def main() -> int:
             data = rs_ref.generate_input(rank, world, m, n, k, True, 3, dist="normal")
             out = rs_sub.custom_kernel(data)
             ok, msg = rs_ref.check_implementation(data, out)
+            ctx = rs_sub.get_context(m, n, dev)
+            ctx.status.zero_()
             f = timed(lambda: rs_sub.custom_kernel(data))
             fmin = timed.last_min
+            words = timing_words(ctx)
             b = timed(lambda: rs_base.custom_kernel(data))
             record("gemm_rs", {"m": m, "n": n, "k": k}, f, b, ok, rf.gemm_rs_roofline_us(m, n, k, world, nominal),
-                   rf.gemm_rs_roofline_us(m, n, k, world, measured), fmin, msg)
+                   rf.gemm_rs_roofline_us(m, n, k, world, measured), fmin, msg, words)
         rs_sub.release_contexts()
     if "ag_gemm" in ops:
         for (m, n, k) in pick("ag_gemm", AG_GEMM_SHAPES):
@@ -134,11 +152,14 @@ def main() -> int:
             data = ag_ref.generate_input(rank, world, m, n, k, True, 5)
             out = ag_sub.custom_kernel(data)
             ok, msg = ag_ref.check_implementation(data, out)
+            ctx = ag_sub.get_context(m, k, dev)
+            ctx.status.zero_()
             f = timed(lambda: ag_sub.custom_kernel(data))
             fmin = timed.last_min
+            words = timing_words(ctx)
             b = timed(lambda: ag_base.custom_kernel(data))
             record("ag_gemm", {"m": m, "n": n, "k": k}, f, b, ok, rf.ag_gemm_roofline_us(m, n, k, world, nominal),
-                   rf.ag_gemm_roofline_us(m, n, k, world, measured), fmin, msg)
+                   rf.ag_gemm_roofline_us(m, n, k, world, measured), fmin, msg, words)
         ag_sub.release_contexts()
     if rank == 0 and ns.out:
         with open(ns.out, "w") as fh:
