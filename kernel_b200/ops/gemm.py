@@ -40,12 +40,46 @@ def _launch(args: N.GemmArgs, device: torch.device) -> None:
     launch_count += 1
 
 
+_NO_PAIR_BIT = 1 << 30
+_pair_choice: dict = {}  # (M, N, K) -> True if the CTA-pair kernel is the faster one on this device
+
+
+def _tuned_pair(args: N.GemmArgs, device: torch.device) -> bool:
+    """Single-rank calls pick between the two tile configurations by timing both
+    once per shape (three launches each, CUDA events); which one wins depends on
+    the shape (pairs win at K around 4096, the single-CTA kernel at very large K)."""
+    key = (args.M, args.N, args.K)
+    hit = _pair_choice.get(key)
+    if hit is not None:
+        return hit
+    if args.M < 256 or os.environ.get("KB200_GEMM_NO_PAIR") == "1":
+        _pair_choice[key] = False
+        return False
+    base = args.num_ctas & ~_NO_PAIR_BIT
+    times = {}
+    for use_pair in (True, False):
+        args.num_ctas = base | (0 if use_pair else _NO_PAIR_BIT)
+        _launch(args, device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            _launch(args, device)
+        e1.record()
+        e1.synchronize()
+        times[use_pair] = e0.elapsed_time(e1)
+    args.num_ctas = base
+    _pair_choice[key] = times[True] <= times[False]
+    return _pair_choice[key]
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-         bias_scale: float = 1.0, status: Optional[torch.Tensor] = None, num_ctas: int = 0, pair: bool = True) -> torch.Tensor:
+         bias_scale: float = 1.0, status: Optional[torch.Tensor] = None, num_ctas: int = 0,
+         pair: Optional[bool] = None) -> torch.Tensor:
     """``out[M,N] = a[M,K] @ b[N,K]^T (+ bias_scale * bias)`` in bf16 with fp32 accumulation.
 
-    ``pair=False`` forces the single-CTA 128x256 kernel; by default two CTAs of a
-    cluster share 256x256 tiles (``cta_group::2``) when M >= 256."""
+    ``pair=True`` uses clusters of two CTAs sharing 256x256 tiles (``cta_group::2``,
+    M >= 256), ``pair=False`` the single-CTA 128x256 kernel, ``None`` times both
+    once per shape and keeps the faster."""
     _check_bf16_2d(a, "a")
     _check_bf16_2d(b, "b")
     M, K = a.shape
@@ -72,7 +106,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, 
     args.rank, args.world, args.epoch = 0, 1, 1
     args.status = status.data_ptr() if status is not None else None
     args.wait_limit_ns = _WAIT_LIMIT_NS
-    args.num_ctas = num_ctas | (0 if pair else (1 << 30))
+    args.num_ctas = num_ctas
+    if pair is None:
+        pair = _tuned_pair(args, a.device)
+    args.num_ctas = num_ctas | (0 if pair else _NO_PAIR_BIT)
     _launch(args, a.device)
     return out
 
@@ -149,6 +186,9 @@ class GemmRS:
         args.bias = bias.data_ptr() if bias is not None else None
         args.bias_scale = bias_scale
         args.epoch = self.epoch
+        if self.world == 1:
+            args.num_ctas = 0
+            args.num_ctas = 0 if _tuned_pair(args, a.device) else _NO_PAIR_BIT
         _launch(args, a.device)
         return out
 
@@ -224,5 +264,8 @@ class AGGemm:
         args.A, args.B, args.out = a_local.data_ptr(), w.data_ptr(), out.data_ptr()
         args.bias = bias.data_ptr() if bias is not None else None
         args.epoch = self.epoch
+        if self.world == 1:
+            args.num_ctas = 0
+            args.num_ctas = 0 if _tuned_pair(args, a_local.device) else _NO_PAIR_BIT
         _launch(args, a_local.device)
         return out

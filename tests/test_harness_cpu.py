@@ -95,3 +95,20 @@ def test_yaml_input_with_world_override(tmp_path):
     rc, log, err = _run(["test", "--yaml", str(yml), "--world", "2", "--backend", "gloo", "--task", "gemm_rs"], "", tmp_path)
     assert rc == 0, err
     assert log["check"] == "pass"
+
+
+def test_leaderboard_mode_rechecks_with_fresh_seeds(tmp_path):
+    rc, log, err = _run(["leaderboard", "@tests", "--backend", "gloo"], RS + "\n", tmp_path)
+    assert rc == 0, err
+    assert log["benchmark-count"] == "1" and log["check"] == "pass"
+    assert int(log["benchmark.0.runs"]) >= 3
+
+
+def test_leaderboard_mode_reports_failure_exit_code(tmp_path):
+    (tmp_path / "wrong_sub2.py").write_text(
+        "from kernel_b200.tasks.gemm_rs.submission import custom_kernel as good\n"
+        "def custom_kernel(data):\n    return good(data) * 0\n")
+    case = "world_size: 2; m: 64; n: 128; k: 256; has_bias: True; seed: 3; dist: normal"
+    rc, log, err = _run(["leaderboard", "@tests", "--backend", "gloo", "--submission", "wrong_sub2"], case + "\n", tmp_path,
+                        env_extra={"PYTHONPATH": f"{ROOT}:{tmp_path}"})
+    assert rc == 112 and log["check"] == "fail"  # the reference falls off main() here and exits 0
