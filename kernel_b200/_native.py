@@ -112,6 +112,7 @@ def _declare(lib: C.CDLL) -> None:
         "kb_wait_flags": (i, [vp, i, u32, u64, vp, vp]),
         "kb_device_barrier": (i, [C.POINTER(vp), u64, i, i, u32, u64, vp, vp]),
         "kb_gemm": (i, [C.POINTER(GemmArgs), vp]),
+        "kb_gemm_schedule": (i, [i, i, i, i, i, i, i, C.POINTER(i), C.POINTER(i)]),
         "kb_gemm_rs_data_bytes": (u64, [i, i, i]),
         "kb_gemm_rs_flag_bytes": (u64, [i, i, i]),
         "kb_gemm_ag_data_bytes": (u64, [i, i]),

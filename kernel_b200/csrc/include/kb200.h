@@ -109,6 +109,8 @@ typedef struct KbGemmArgs {
 } KbGemmArgs;
 
 int kb_gemm(const KbGemmArgs* args, void* stream);
+// Host replica of the kernel's static tile schedule (tests of the index arithmetic).
+int kb_gemm_schedule(int mode, int M, int N, int rank, int world, int pair, int pos, int* block, int* nb);
 // Bytes each rank needs in the symmetric heap for the given problem.
 uint64_t kb_gemm_rs_data_bytes(int M, int N, int world);
 uint64_t kb_gemm_rs_flag_bytes(int M, int N, int world);

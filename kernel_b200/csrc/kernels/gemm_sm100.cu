@@ -139,7 +139,7 @@ __device__ __forceinline__ Smem carve(uint8_t* raw) {
 // never has a push queued behind one of its own waits, which is what makes
 // the cross-rank waits deadlock-free.
 template <bool kPair>
-__device__ __forceinline__ void tile_at(const GemmParams& p, int pos, int& mbq, int& nb) {
+__host__ __device__ __forceinline__ void tile_at(const GemmParams& p, int pos, int& mbq, int& nb) {
   constexpr int GROUP_M = Cfg<kPair>::GROUP;
   int start = 0;
   int first_len = p.MBQ;  // blocks in the first segment
@@ -671,43 +671,48 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
   } else if (kAG && warp >= 8) {
     // -------------------------------------------------- all-gather pusher ----
     const int ct = tid - 256;
-    // Row block by row block, all CTAs together: each takes an equal slice of the
-    // block's bytes (rows are contiguous in the input and in the gather buffers),
-    // reads it once and stores it into the gather buffer of every other rank
-    // (and of this rank, unless the GEMM reads its own rows in place).  Blocks
-    // therefore arrive everywhere in ascending order, which is the order in
-    // which the GEMMs consume them.  The last CTA to finish its slice of a block
-    // releases the block's flag on every rank.
+    // Group of row blocks by group, all CTAs together.  A group is cut into
+    // slices of 1024 vectors (16 KB); CTAs claim slices from a counter, so an SM
+    // with a slower path to the links simply takes fewer of them and the group
+    // completes at the aggregate rate instead of the slowest SM's.  A claimed
+    // slice is read once (eight 16-byte loads per thread in flight) and stored
+    // into the gather buffer of every other rank (and of this rank, unless the
+    // GEMM reads its own rows in place).  Groups therefore arrive everywhere in
+    // ascending order, which is the order in which the GEMMs consume them.  When
+    // a CTA finds a group exhausted it fences and counts itself done; the last
+    // one releases the group's flags on every rank and rewinds the claim counter.
     const int n_chunks = p.own_hi_mb - p.own_lo_mb + 1;
     const int own_row0 = p.rank * p.rpo;
     const int dd0 = p.ag_own_direct ? 1 : 0;
-    uint32_t* counters = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.counter_off);
-    // Completion (CTA barrier, system fence, counter) is paid once per group of
-    // row blocks, at most eight times per call.
-    const int group = (n_chunks + 7) / 8;
-    for (int c = 0; c < n_chunks; ++c) {
-      const int mb = p.own_lo_mb + c;
-      int r_begin = mb * BM;
+    uint32_t* counters = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.counter_off);  // [0..63] done, [64..127] claim
+    const int group = (n_chunks + 7) / 8;  // at most eight groups per call
+    const int n_groups = (n_chunks + group - 1) / group;
+    constexpr size_t SLICE = 8 * 128;
+    __shared__ uint32_t s_claim;
+    for (int g = 0; g < n_groups; ++g) {
+      const int c_lo = g * group;
+      int c_hi = c_lo + group;
+      if (c_hi > n_chunks) c_hi = n_chunks;
+      int r_begin = (p.own_lo_mb + c_lo) * BM;
       if (r_begin < own_row0) r_begin = own_row0;
-      int r_end = mb * BM + BM;
+      int r_end = (p.own_lo_mb + c_hi) * BM;
       if (r_end > own_row0 + p.rpo) r_end = own_row0 + p.rpo;
       if (r_end > p.M) r_end = p.M;
       const size_t nvec = static_cast<size_t>(r_end - r_begin) * p.K / 8;
-      size_t per = (nvec + gridDim.x - 1) / gridDim.x;
-      per = (per + 127) / 128 * 128;
-      size_t lo = static_cast<size_t>(blockIdx.x) * per;
-      size_t hi = lo + per;
-      if (lo > nvec) lo = nvec;
-      if (hi > nvec) hi = nvec;
+      const uint32_t n_slices = static_cast<uint32_t>((nvec + SLICE - 1) / SLICE);
       const uint4* src = reinterpret_cast<const uint4*>(p.a_local + static_cast<size_t>(r_begin - own_row0) * p.K);
-      // Up to eight independent 16-byte loads per thread are in flight before the
-      // first store, whatever the length of the slice.
-      for (size_t base = lo; base < hi; base += 8 * 128) {
+      for (;;) {
+        if (ct == 0) s_claim = atomicAdd(&counters[64 + g], 1u);
+        comm_bar_sync();
+        const uint32_t slice = s_claim;
+        comm_bar_sync();  // everybody has read the claim before thread 0 overwrites it
+        if (slice >= n_slices) break;
+        const size_t base = static_cast<size_t>(slice) * SLICE;
         uint4 x[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const size_t v = base + u * 128 + ct;
-          if (v < hi) x[u] = kb::ld_nc_v4(src + v);
+          if (v < nvec) x[u] = kb::ld_nc_v4(src + v);
         }
         for (int dd = dd0; dd < p.world; ++dd) {
           const int dst = (p.rank - dd + p.world) % p.world;
@@ -715,20 +720,17 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             const size_t v = base + u * 128 + ct;
-            if (v < hi) kb::st_sys_v4(dstp + v, x[u]);
+            if (v < nvec) kb::st_sys_v4(dstp + v, x[u]);
           }
         }
       }
-      const bool group_end = ((c + 1) % group == 0) || (c + 1 == n_chunks);
-      if (!group_end) continue;
-      comm_bar_sync();
       if (ct == 0) {
         kb::fence_sys();
-        const int g = c / group;
         const uint32_t old = atomicAdd(&counters[g], 1u);
         if ((old + 1u) % gridDim.x == 0u) {
+          counters[64 + g] = 0u;  // every CTA is past its last claim of this group
           kb::fence_sys();
-          for (int cc = g * group; cc <= c; ++cc) {
+          for (int cc = c_lo; cc < c_hi; ++cc) {
             for (int dd = dd0; dd < p.world; ++dd) {
               const int dst = (p.rank - dd + p.world) % p.world;
               kb::st_relaxed_sys_u32(ag_flag(p, dst, p.rank, p.own_lo_mb + cc), p.epoch);
@@ -780,6 +782,36 @@ inline bool getenv_flag(const char* name) {
 
 }  // namespace
 
+// Host replica of the device tile schedule, for tests of the index arithmetic:
+// position -> (scheduling block, column block) for the given problem and rank.
+// Returns the number of positions, or -1 for invalid arguments.
+extern "C" int kb_gemm_schedule(int mode, int M, int N, int rank, int world, int pair, int pos, int* block, int* nb) {
+  if (M <= 0 || N <= 0 || world < 1 || rank < 0 || rank >= world || (mode != KB_GEMM_PLAIN && M % world != 0)) return -1;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.mode = world > 1 ? mode : KB_GEMM_PLAIN;
+  p.M = M;
+  p.N = N;
+  p.world = world;
+  p.rank = rank;
+  p.MB = (M + BM - 1) / BM;
+  p.NB = (N + BN - 1) / BN;
+  p.rpo = (p.mode == KB_GEMM_PLAIN) ? M : M / world;
+  const int block_rows = pair ? 256 : 128;
+  const bool dist_mode = p.mode != KB_GEMM_PLAIN;
+  if (pair && dist_mode && (p.rpo % 256) != 0) return -1;
+  p.MBQ = (M + block_rows - 1) / block_rows;
+  p.own_lo_q = dist_mode ? (rank * p.rpo) / block_rows : 0;
+  p.own_hi_q = dist_mode ? ((rank + 1) * p.rpo - 1) / block_rows : p.MBQ - 1;
+  p.ag_n_own = (p.mode == KB_GEMM_AG && (p.rpo % block_rows) == 0) ? p.rpo / block_rows : 0;
+  const int total = p.MBQ * p.NB;
+  if (pos >= 0 && pos < total && block != nullptr && nb != nullptr) {
+    if (pair) tile_at<true>(p, pos, *block, *nb);
+    else tile_at<false>(p, pos, *block, *nb);
+  }
+  return total;
+}
+
 extern "C" uint64_t kb_gemm_rs_data_bytes(int M, int N, int world) {
   return round_up(2ull * world * (uint64_t)(M / world) * N * 2, 256);
 }
@@ -792,7 +824,9 @@ extern "C" uint64_t kb_gemm_ag_flag_bytes(int M, int world) {
   return round_up(2ull * world * ((M + BM - 1) / BM) * 4, 256);
 }
 extern "C" uint64_t kb_gemm_ag_counter_bytes(int M, int world) {
-  return round_up((uint64_t)world * ((M + BM - 1) / BM + 1) * 4, 256);
+  (void)M;
+  (void)world;
+  return 1024;  // 64 completion counters and 64 claim counters (at most eight groups are used)
 }
 
 extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {

@@ -1,0 +1,79 @@
+"""The GEMM kernels' static tile schedule, checked on the host replica of the
+device function: every tile exactly once, the rows a rank owns last for the
+reduce-scatter, own rows first and arrival order after that for the all-gather."""
+import ctypes as C
+
+import pytest
+
+from kernel_b200 import _native as N
+
+PLAIN, RS, AG = 0, 1, 2
+
+
+def schedule(mode, M, Nn, rank, world, pair):
+    lib = N.lib()
+    total = lib.kb_gemm_schedule(mode, M, Nn, rank, world, int(pair), -1, None, None)
+    if total < 0:
+        return None
+    blk, nb = C.c_int(), C.c_int()
+    out = []
+    for pos in range(total):
+        lib.kb_gemm_schedule(mode, M, Nn, rank, world, int(pair), pos, C.byref(blk), C.byref(nb))
+        out.append((blk.value, nb.value))
+    return out
+
+
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("M,Nn,world", [(8192, 8192, 8), (2048, 4096, 8), (4096, 2880, 2), (16384, 4096, 8), (1000, 1000, 1), (8192, 29568, 1)])
+@pytest.mark.parametrize("mode", [PLAIN, RS, AG])
+def test_every_tile_exactly_once(mode, M, Nn, world, pair):
+    rows = 256 if pair else 128
+    for rank in range(world):
+        tiles = schedule(mode, M, Nn, rank, world, pair)
+        if tiles is None:
+            assert pair and (M // world) % 256 != 0
+            continue
+        mbq, nbs = -(-M // rows), -(-Nn // 256)
+        assert len(tiles) == mbq * nbs and len(set(tiles)) == len(tiles)
+        assert all(0 <= b < mbq and 0 <= n < nbs for b, n in tiles)
+
+
+@pytest.mark.parametrize("pair", [False, True])
+def test_reduce_scatter_visits_own_rows_last(pair):
+    M, Nn, world = 8192, 8192, 8
+    rows = 256 if pair else 128
+    per_rank = M // world // rows
+    nbs = Nn // 256
+    for rank in range(world):
+        tiles = schedule(RS, M, Nn, rank, world, pair)
+        own = set(range(rank * per_rank, (rank + 1) * per_rank))
+        tail = tiles[-per_rank * nbs:]
+        assert {b for b, _ in tail} == own
+        assert not ({b for b, _ in tiles[:-per_rank * nbs]} & own)
+        # the sweep starts with the rows of the next rank, so that every owner is fed by a different peer
+        assert tiles[0][0] == ((rank + 1) % world) * per_rank
+
+
+def test_small_m_reduce_scatter_single_block_holds_all_owners():
+    tiles = schedule(RS, 64, 2880, 3, 8, False)  # 8 rows per rank: one row block for everybody
+    assert {b for b, _ in tiles} == {0} and len(tiles) == 12
+
+
+@pytest.mark.parametrize("pair", [False, True])
+def test_all_gather_order_own_first_then_arrival_order(pair):
+    M, Nn, world = 8192, 3696, 8
+    rows = 256 if pair else 128
+    per_rank = M // world // rows
+    for rank in range(world):
+        tiles = schedule(AG, M, Nn, rank, world, pair)
+        seq = []
+        for b, _ in tiles:  # order in which row blocks first appear
+            if b not in seq:
+                seq.append(b)
+        assert seq[:per_rank] == list(range(rank * per_rank, (rank + 1) * per_rank))
+        rest = seq[per_rank:]
+        # block c of every other source before block c+1 of any source
+        chunk_index = [b % per_rank for b in rest]
+        assert chunk_index == sorted(chunk_index)
+        first_round = rest[:world - 1]
+        assert [b // per_rank for b in first_round] == [(rank + d) % world for d in range(1, world)]
