@@ -46,7 +46,7 @@ _pair_choice: dict = {}  # (M, N, K) -> True if the CTA-pair kernel is the faste
 
 def _tuned_pair(args: N.GemmArgs, device: torch.device) -> bool:
     """Single-rank calls pick between the two tile configurations by timing both
-    once per shape (three launches each, CUDA events); which one wins depends on
+    once per shape (three alternating launches each, CUDA events); which one wins depends on
     the shape (pairs win at K around 4096, the single-CTA kernel at very large K)."""
     key = (args.M, args.N, args.K)
     hit = _pair_choice.get(key)
@@ -56,17 +56,23 @@ def _tuned_pair(args: N.GemmArgs, device: torch.device) -> bool:
         _pair_choice[key] = False
         return False
     base = args.num_ctas & ~_NO_PAIR_BIT
-    times = {}
-    for use_pair in (True, False):
+    times = {True: 0.0, False: 0.0}
+
+    def run(use_pair: bool) -> None:
         args.num_ctas = base | (0 if use_pair else _NO_PAIR_BIT)
         _launch(args, device)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(3):
-            _launch(args, device)
-        e1.record()
-        e1.synchronize()
-        times[use_pair] = e0.elapsed_time(e1)
+
+    for use_pair in (True, False, True, False):  # warm up both; the clocks settle under load
+        run(use_pair)
+    # Alternate the two so that neither is measured on a cooler, faster-clocked GPU.
+    for _ in range(3):
+        for use_pair in (True, False):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run(use_pair)
+            e1.record()
+            e1.synchronize()
+            times[use_pair] += e0.elapsed_time(e1)
     args.num_ctas = base
     _pair_choice[key] = times[True] <= times[False]
     return _pair_choice[key]
