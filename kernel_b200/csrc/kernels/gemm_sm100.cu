@@ -50,7 +50,6 @@ struct Cfg {
   static constexpr int STAGES = kPair ? 6 : 4;
   static constexpr int B_ROWS = kPair ? 128 : 256;
   static constexpr int B_BYTES = B_ROWS * BK * 2;
-  static constexpr int GROUP = kPair ? 4 : 8;  // scheduling blocks swept together (1024 rows)
 };
 constexpr int MAX_STAGES = 6;
 constexpr int EPI_COLS = 128;                 // columns staged per epilogue pass
@@ -83,6 +82,7 @@ struct alignas(64) GemmParams {
   int ag_parts;
   // Scheduling blocks: 128 rows (single CTA) or 256 rows (CTA pair).
   int MBQ, own_lo_q, own_hi_q;
+  int group;  // scheduling blocks swept together (rasterisation)
   int ag_own_direct;  // AG: own row blocks are loaded straight from the input (no self copy)
   int ag_n_own;  // AG: scheduling blocks per source when they tile the rows evenly, else 0 (plain rotated order)
   int debug;  // experiments only (KB200_GEMM_DEBUG): 1 no global stores, 2 epilogue only releases TMEM, 4 every load reads tile (0,0), 8 timing words: status[5] max us waited on peers, [6] us until the pushes were out, [7] us until the last epilogue
@@ -140,7 +140,7 @@ __device__ __forceinline__ Smem carve(uint8_t* raw) {
 // the cross-rank waits deadlock-free.
 template <bool kPair>
 __host__ __device__ __forceinline__ void tile_at(const GemmParams& p, int pos, int& mbq, int& nb) {
-  constexpr int GROUP_M = Cfg<kPair>::GROUP;
+  const int GROUP_M = p.group;
   int start = 0;
   int first_len = p.MBQ;  // blocks in the first segment
   if (p.mode == KB_GEMM_RS) {
@@ -804,6 +804,10 @@ extern "C" int kb_gemm_schedule(int mode, int M, int N, int rank, int world, int
   p.own_lo_q = dist_mode ? (rank * p.rpo) / block_rows : 0;
   p.own_hi_q = dist_mode ? ((rank + 1) * p.rpo - 1) / block_rows : p.MBQ - 1;
   p.ag_n_own = (p.mode == KB_GEMM_AG && (p.rpo % block_rows) == 0) ? p.rpo / block_rows : 0;
+  // 1024 rows are swept together (measured best among 512 to 4096 on 8192 x 8192 x 29568; for the all-gather
+  // kernel it also makes the first group consist of this rank's own rows only at eight ranks).
+  p.group = 1024 / block_rows;
+  if (const char* g = getenv("KB200_GEMM_GROUP")) p.group = atoi(g) > 0 ? atoi(g) : p.group;
   const int total = p.MBQ * p.NB;
   if (pos >= 0 && pos < total && block != nullptr && nb != nullptr) {
     if (pair) tile_at<true>(p, pos, *block, *nb);
@@ -934,6 +938,10 @@ extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {
   p.own_lo_q = dist_mode ? (a->rank * p.rpo) / block_rows : 0;
   p.own_hi_q = dist_mode ? ((a->rank + 1) * p.rpo - 1) / block_rows : p.MBQ - 1;
   p.ag_n_own = (p.mode == KB_GEMM_AG && (p.rpo % block_rows) == 0) ? p.rpo / block_rows : 0;
+  // 1024 rows are swept together (measured best among 512 to 4096 on 8192 x 8192 x 29568; for the all-gather
+  // kernel it also makes the first group consist of this rank's own rows only at eight ranks).
+  p.group = 1024 / block_rows;
+  if (const char* g = getenv("KB200_GEMM_GROUP")) p.group = atoi(g) > 0 ? atoi(g) : p.group;
 
   int rc = make_tmap(&p.tmA, a_ptr, a_rows, a->K, BM);
   if (rc != KB_OK) return rc;
