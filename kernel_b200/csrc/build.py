@@ -25,6 +25,7 @@ SOURCES = [
     "common/host_util.cpp",
     "symm/fd_exchange.cpp",
     "symm/symm_heap.cpp",
+    "symm/a2a_host.cpp",
     "kernels/a2a.cu",
     "kernels/gemm_sm100.cu",
 ]

@@ -57,7 +57,12 @@ class MoEAllToAll:
         self.native = torch.cuda.is_available() and (device is None or torch.device(device).type == "cuda")
         self.epoch = 0
         self.heap = None
-        if self.native:
+        self._trace = None
+        # CPU ranks: the same protocol over a memfd-backed symmetric heap (bf16 and
+        # fp32), or torch.distributed collectives (any dtype; KB200_A2A_CPU_PATH=collectives).
+        self.host_heap = (not self.native and dtype in (torch.bfloat16, torch.float32)
+                          and os.environ.get("KB200_A2A_CPU_PATH", "heap") == "heap")
+        if self.native or self.host_heap:
             if dtype not in _DTYPES:
                 raise ValueError(f"unsupported dtype {dtype}")
             lib = N.lib()
@@ -65,7 +70,8 @@ class MoEAllToAll:
             rows = int(lib.kb_a2a_rows_bytes(self.world, max_num_tokens, experts_per_token, hidden_dim, eb))
             counts = (self.world * self.El * 4 + 255) // 256 * 256
             need = 2 * rows + counts + 256 + 256 + 4096
-            self.heap = heap or SymmHeap(need, group=group, device=device)
+            self.heap = heap or (SymmHeap(need, group=group, device=device) if self.native
+                                 else SymmHeap(need, group=group, backend="host", timeout_s=_WAIT_LIMIT_NS / 1e9 + 5))
             self.recv_off = self.heap.alloc(rows)
             self.y_off = self.heap.alloc(rows)
             self.count_off = self.heap.alloc(counts)
@@ -136,6 +142,12 @@ class MoEAllToAll:
         """Full round trip with the simulated expert ``y = scale(expert) * x``."""
         self._validate(x, indices, weights)
         if not x.is_cuda:
+            if self.host_heap:
+                out = torch.empty_like(x)
+                self.epoch += 1
+                a = self._args(x, indices, weights, out, scale_mode)
+                N.check(self._lib.kb_a2a_round_trip_host(C.byref(a), max(1, _WAIT_LIMIT_NS // 1_000_000)))
+                return out
             return self._cpu_round_trip(x, indices, weights, scale_mode)
         global launch_count
         out = torch.empty_like(x)

@@ -100,3 +100,58 @@ def test_bad_arguments_are_rejected_with_a_message():
     assert lib.kb_symm_create(N.BACKEND_HOST, 3, 2, 4096, 0, C.byref(h)) == N.KB_ERR_ARG
     assert "bad arguments" in N.last_error()
     assert lib.kb_symm_create(99, 0, 1, 4096, 0, C.byref(h)) == N.KB_ERR_ARG
+
+
+def _moe_over_host_heap(rank, world, dtype_name):
+    """The MoE round trip of CPU ranks runs the kernels' protocol (slots, peer
+    stores, epoch flags, pull combine) over the memfd-backed heap."""
+    import torch
+
+    from kernel_b200.ops.dispatch_combine import SCALE_EXPERT, MoEAllToAll, expert_scale_vector
+
+    dtype = {"fp32": torch.float32, "bf16": torch.bfloat16}[dtype_name]
+    E, k, H, T = 18, 4, 64, 5 + rank  # token counts differ between ranks
+    ctx = MoEAllToAll(E, k, H, 16, dtype=dtype, device="cpu")
+    assert ctx.host_heap and ctx.heap.backend == "host"
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(T, H, generator=g).to(dtype)
+    idx = torch.rand(T, E, generator=g).argsort(1)[:, :k].to(torch.int32).contiguous()
+    w = torch.softmax(torch.randn(T, k, generator=g), -1)
+    outs = [ctx.dispatch_scale_combine(x, idx, w, SCALE_EXPERT) for _ in range(3)]  # three epochs on one workspace
+    sc = expert_scale_vector(E, world, SCALE_EXPERT)[idx.long()]
+    y = (x.float().unsqueeze(1) * sc.unsqueeze(-1)).to(dtype).float()
+    ref = (y * w.unsqueeze(-1)).sum(1)
+    tol = dict(rtol=1e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=1e-2, atol=5e-3)
+    ok = all(torch.allclose(o.float(), ref, **tol) for o in outs) and torch.equal(outs[0], outs[2])
+    ctx.heap.close()
+    return bool(ok)
+
+
+@pytest.mark.parametrize("dtype_name", ["fp32", "bf16"])
+def test_moe_round_trip_over_host_heap(dtype_name):
+    assert all(run_ranks(_moe_over_host_heap, 3, dtype_name))
+
+
+def _moe_with_absent_rank(rank, world):
+    import torch
+
+    from kernel_b200.ops.dispatch_combine import MoEAllToAll
+
+    ctx = MoEAllToAll(8, 2, 32, 4, dtype=torch.float32, device="cpu")
+    x = torch.randn(4, 32)
+    idx = torch.tensor([[0, 5], [1, 4], [2, 7], [3, 6]], dtype=torch.int32)
+    w = torch.full((4, 2), 0.5)
+    ctx.dispatch_scale_combine(x, idx, w)  # epoch 1: everybody takes part
+    if rank == 1:
+        return "absent"  # epoch 2: this rank never calls
+    try:
+        ctx.dispatch_scale_combine(x, idx, w)
+    except N.SymmTimeoutError as e:
+        return str(e)
+    return "no error"
+
+
+def test_moe_wait_names_the_rank_that_never_arrived():
+    res = run_ranks(_moe_with_absent_rank, 2, env={"KB200_WAIT_LIMIT_MS": "300"})
+    assert res[1] == "absent"
+    assert "rank 1 never finished its dispatch of epoch 2" in res[0]
