@@ -227,6 +227,31 @@ class MoEAllToAll:
         launch_count += 2
         return out
 
+    # ------------------------------------------------------- debug checks ----
+    _POISON = 0x7FC1  # a bf16/fp16 NaN bit pattern that no kernel produces
+
+    def poison_workspace(self) -> None:
+        """Fills both row regions of this rank with a sentinel.  Together with
+        ``verify_workspace`` this is the stand-in for a memory checker: after a
+        call no sentinel may survive inside the rows the counts declare valid,
+        and nothing may have been written outside them."""
+        nbytes = self.world * self.cap * self.H * self._eb
+        for off in (self.recv_off, self.y_off):
+            self.heap.tensor(off, (nbytes // 2,), torch.int16).fill_(self._POISON)
+
+    def verify_workspace(self) -> Tuple[int, int]:
+        """Returns ``(sentinel words inside valid rows, written words outside valid
+        rows)`` for this rank's receive region; both must be zero.  Synchronises."""
+        counts = self.heap.tensor(self.count_off, (self.world, self.El), torch.int32).clone()
+        words_per_row = self.H * self._eb // 2
+        recv = self.heap.tensor(self.recv_off, (self.world, self.cap, words_per_row), torch.int16)
+        is_poison = recv == (self._POISON)
+        totals = counts.sum(1)
+        valid = torch.arange(self.cap, device=recv.device).unsqueeze(0) < totals.unsqueeze(1)  # [world, cap]
+        inside = int((is_poison & valid.unsqueeze(-1)).sum())
+        outside = int((~is_poison & ~valid.unsqueeze(-1)).sum())
+        return inside, outside
+
     def expert_view(self, counts: torch.Tensor, recv: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """Expert-major padded view ``(expert_num_tokens [El], expert_x [El, max_recv, H])``
         like ``PyTorchAllToAll.dispatch`` returns (reference.py:123-148).  Copies."""

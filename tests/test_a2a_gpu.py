@@ -111,3 +111,21 @@ def test_argument_validation():
     x5, idx5, w5 = _inputs(8, 2, 128, 5, torch.bfloat16, dev)
     with pytest.raises(ValueError):
         ctx.dispatch_scale_combine(x5, idx5, w5)
+
+
+def test_sentinel_and_guard_rows_after_dispatch():
+    """Poisoned workspace: every row the counts declare valid was written, nothing
+    else was touched (the role a memory checker would play)."""
+    from kernel_b200.ops.dispatch_combine import MoEAllToAll
+
+    E, k, H, T = 32, 4, 1024, 50
+    dev = torch.device("cuda")
+    ctx = MoEAllToAll(E, k, H, 64, dtype=torch.bfloat16, device=dev)  # capacity 256 rows, 200 used
+    x, idx, w = _inputs(E, k, H, T, torch.bfloat16, dev, seed=9)
+    ctx.poison_workspace()
+    out = ctx.dispatch_scale_combine(x, idx, w, 2)
+    torch.cuda.synchronize()
+    ctx.heap.check_status()
+    inside, outside = ctx.verify_workspace()
+    assert inside == 0 and outside == 0
+    assert torch.isfinite(out.float()).all()
