@@ -22,7 +22,10 @@ What differs from the reference, on purpose:
   case keys otherwise), the implementation is selectable (``--impl
   fused|baseline`` or ``--submission some.module``) and the backend/device are parameters (``--backend
   nccl|gloo``), so the same flow runs on CPU ranks;
-* a tests file may be replaced by ``--yaml <task.yml> --section tests|benchmarks``.
+* a tests file may be replaced by ``--yaml <task.yml> --section tests|benchmarks``;
+* benchmark modes log, besides the reference's six keys, ``max_rank_us``,
+  ``roofline_us`` / ``roofline_frac`` and with ``--with-baseline`` also
+  ``baseline_us`` / ``speedup``; ``--json FILE`` dumps the rows.
 """
 from __future__ import annotations
 
@@ -415,10 +418,46 @@ class Runner:
         return [p.get(BENCH_TIMEOUT_S) for p in pending][0]
 
 
-def _log_stats(logger: PopcornOutput, idx: int, stats: Stats) -> None:
+def case_roofline_us(task: str, args: dict) -> Optional[float]:
+    """Roofline of a case in microseconds (slower of FLOPs at the nominal bf16 peak
+    and NVLink bytes at 900 GB/s per direction), or None if the keys are missing."""
+    from ..utils import roofline as rf
+
+    try:
+        world = int(args.get("world_size", 1))
+        if task == "all2all":
+            eb = 4 if str(args.get("dtype", "fp16")) in ("fp32", "float32") else 2
+            return rf.a2a_roofline_us(args["max_num_tokens"], args["experts_per_token"], args["hidden_dim"], eb, world)["roofline_us"]
+        if task == "gemm_rs":
+            return rf.gemm_rs_roofline_us(args["m"], args["n"], args["k"], world)["roofline_us"]
+        if task == "ag_gemm":
+            return rf.ag_gemm_roofline_us(args["m"], args["n"], args["k"], world)["roofline_us"]
+    except (KeyError, ZeroDivisionError):
+        pass
+    return None
+
+
+def _log_stats(logger: PopcornOutput, idx: int, stats: Stats, task: Optional[str] = None, args: Optional[dict] = None,
+               baseline: Optional[Stats] = None) -> dict:
+    """Logs the reference's six keys (ns) plus, in microseconds, ``max_rank_us``,
+    ``roofline_us`` / ``roofline_frac`` and, when a baseline was timed,
+    ``baseline_us`` / ``speedup``.  Returns the row for the JSON dump."""
+    row = {}
     for field in dataclasses.fields(Stats):
         logger.log(f"benchmark.{idx}.{field.name}", getattr(stats, field.name))
-    logger.log(f"benchmark.{idx}.max_rank_us", stats.mean / 1e3)
+        row[field.name] = getattr(stats, field.name)
+    row["max_rank_us"] = stats.mean / 1e3
+    logger.log(f"benchmark.{idx}.max_rank_us", row["max_rank_us"])
+    roof = case_roofline_us(task, args) if task and args else None
+    if roof is not None and stats.mean > 0:
+        row["roofline_us"], row["roofline_frac"] = roof, roof / row["max_rank_us"]
+        logger.log(f"benchmark.{idx}.roofline_us", roof)
+        logger.log(f"benchmark.{idx}.roofline_frac", row["roofline_frac"])
+    if baseline is not None:
+        row["baseline_us"], row["speedup"] = baseline.mean / 1e3, baseline.mean / stats.mean
+        logger.log(f"benchmark.{idx}.baseline_us", row["baseline_us"])
+        logger.log(f"benchmark.{idx}.speedup", row["speedup"])
+    return row
 
 
 def run_testing(logger: PopcornOutput, runner: Runner, tests: List[TestCase]) -> int:
@@ -439,21 +478,31 @@ def run_testing(logger: PopcornOutput, runner: Runner, tests: List[TestCase]) ->
     return EXIT_OK if passed else EXIT_FAIL
 
 
-def run_benchmarking(logger: PopcornOutput, runner: Runner, tests: List[TestCase], leaderboard: bool) -> int:
+def run_benchmarking(logger: PopcornOutput, runner: Runner, tests: List[TestCase], leaderboard: bool,
+                     baseline_runner: Optional[Runner] = None, json_path: Optional[str] = None) -> int:
     runner.benchmark(tests[0], False, 100, 1e7 if leaderboard else 1e8)  # warm-up
     logger.log("benchmark-count", len(tests))
     passed = True
+    rows = []
     for idx, test in enumerate(tests):
         logger.log(f"benchmark.{idx}.spec", test.spec)
         result = runner.benchmark(test, leaderboard, 100, 30e9 if leaderboard else 10e9)
         if isinstance(result, Stats):
-            _log_stats(logger, idx, result)
+            base = None
+            if baseline_runner is not None:
+                b = baseline_runner.benchmark(test, False, 100, 10e9)
+                base = b if isinstance(b, Stats) else None
+            row = _log_stats(logger, idx, result, runner.task or guess_task(test.args), test.args, base)
+            rows.append({"spec": test.spec, **row})
         else:
             passed = False
             logger.log(f"benchmark.{idx}.status", "fail")
             logger.log(f"benchmark.{idx}.error", str(result))
+            rows.append({"spec": test.spec, "error": str(result)})
             if leaderboard:
                 break
+    if json_path:
+        Path(json_path).write_text(json.dumps(rows, indent=1))
     logger.log("check", "pass" if passed else "fail")
     return EXIT_OK if passed else EXIT_FAIL
 
@@ -482,6 +531,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--yaml")
     ap.add_argument("--section", default=None)
     ap.add_argument("--world", type=int, default=None, help="override world_size of every case")
+    ap.add_argument("--with-baseline", action="store_true", help="benchmark modes: also time the NCCL+cuBLAS baseline and log baseline_us / speedup")
+    ap.add_argument("--json", default=None, help="benchmark modes: also write the rows to this file")
     try:
         ns = ap.parse_args(argv)
     except SystemExit:
@@ -519,10 +570,11 @@ def main(argv: Optional[List[str]] = None) -> int:
             runner = Runner(pool, n_gpus, ns.task, ns.submission or ns.impl, ns.backend)
             if ns.mode == "test":
                 return run_testing(logger, runner, tests)
+            base_runner = Runner(pool, n_gpus, ns.task, "baseline", ns.backend) if ns.with_baseline else None
             if ns.mode == "benchmark":
-                return run_benchmarking(logger, runner, tests, leaderboard=False)
+                return run_benchmarking(logger, runner, tests, False, base_runner, ns.json)
             if ns.mode == "leaderboard":
-                return run_benchmarking(logger, runner, tests, leaderboard=True)
+                return run_benchmarking(logger, runner, tests, True, base_runner, ns.json)
             return run_profiling(logger, runner, tests)
 
 

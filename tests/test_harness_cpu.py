@@ -112,3 +112,19 @@ def test_leaderboard_mode_reports_failure_exit_code(tmp_path):
     rc, log, err = _run(["leaderboard", "@tests", "--backend", "gloo", "--submission", "wrong_sub2"], case + "\n", tmp_path,
                         env_extra={"PYTHONPATH": f"{ROOT}:{tmp_path}"})
     assert rc == 112 and log["check"] == "fail"  # the reference falls off main() here and exits 0
+
+
+def test_benchmark_extra_keys_baseline_and_json(tmp_path):
+    import json
+
+    out = tmp_path / "rows.json"
+    rc, log, err = _run(["benchmark", "@tests", "--backend", "gloo", "--with-baseline", "--json", str(out)], RS + "\n" + A2A + "\n",
+                        tmp_path)
+    assert rc == 0, err
+    for i in range(2):
+        for key in ("max_rank_us", "roofline_us", "roofline_frac", "baseline_us", "speedup"):
+            assert f"benchmark.{i}.{key}" in log, (i, key)
+    rows = json.loads(out.read_text())
+    assert len(rows) == 2 and rows[0]["spec"] == RS and rows[0]["speedup"] > 0
+    # gemm_rs 64 x 128 x 256 on two ranks: link term 64*128*2/2 bytes at 900 GB/s
+    assert abs(rows[0]["roofline_us"] - 64 * 128 * 2 / 2 / 900e9 * 1e6) < 1e-6
