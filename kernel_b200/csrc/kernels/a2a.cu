@@ -165,18 +165,29 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh) {
   __syncthreads();
   stamp(p, ST_SLOTS);
 
-  // Payload: one 16-byte vector per thread, read once, stored k times.
+  // Payload: every 16-byte vector is read once and stored k times.  A thread
+  // first issues all the loads of its (up to four) vectors of a row, so that the
+  // load latency is paid once per row, not once per vector.
   for (int t = t0; t < t1; ++t) {
     const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(t) * p.row_bytes);
-    for (int v = v0 + tid; v < v1; v += blockDim.x) {
-      const uint4 val = kb::ld_nc_v4(src + v);
+    for (int vb = v0 + tid; vb < v1; vb += 4 * blockDim.x) {
+      uint4 val[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = vb + u * blockDim.x;
+        if (v < v1) val[u] = kb::ld_nc_v4(src + v);
+      }
       for (int kk = 0; kk < p.k; ++kk) {
         const int i = (t - t0) * p.k + kk;
         const int slot = ent_slot[i];
         if (slot < 0) continue;
         const int dst = ent_e[i] / p.El;
-        uint4* d = reinterpret_cast<uint4*>(rows_ptr(p, dst, p.recv_off, p.rank, slot)) + v;
-        kb::st_sys_v4(d, val);
+        uint4* d = reinterpret_cast<uint4*>(rows_ptr(p, dst, p.recv_off, p.rank, slot));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int v = vb + u * blockDim.x;
+          if (v < v1) kb::st_sys_v4(d + v, val[u]);
+        }
       }
     }
   }
@@ -311,12 +322,24 @@ __device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh) {
     if (p.scale_mode == 2) scale = static_cast<float>(p.rank * p.El + lo + 1) / static_cast<float>(p.E);
     const uint4* src = reinterpret_cast<const uint4*>(rows_ptr(p, p.rank, p.recv_off, s, row));
     uint4* dst = reinterpret_cast<uint4*>(rows_ptr(p, p.rank, p.y_off, s, row));
-    for (int v = tid; v < p.vecs; v += blockDim.x) {
-      float f[Vec16<T>::N];
-      Vec16<T>::load(kb::ld_sys_v4(src + v), f);
+    for (int vb = tid; vb < p.vecs; vb += 4 * blockDim.x) {
+      uint4 in[4];
 #pragma unroll
-      for (int i = 0; i < Vec16<T>::N; ++i) f[i] *= scale;
-      dst[v] = Vec16<T>::store(f);
+      for (int u = 0; u < 4; ++u) {  // all loads of this thread first: one latency per row
+        const int v = vb + u * blockDim.x;
+        if (v < p.vecs) in[u] = kb::ld_sys_v4(src + v);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = vb + u * blockDim.x;
+        if (v < p.vecs) {
+          float f[Vec16<T>::N];
+          Vec16<T>::load(in[u], f);
+#pragma unroll
+          for (int i = 0; i < Vec16<T>::N; ++i) f[i] *= scale;
+          dst[v] = Vec16<T>::store(f);
+        }
+      }
     }
   }
   stamp(p, ST_EXPERT_ROWS);

@@ -159,13 +159,13 @@ class MoEAllToAll:
         if a is None:
             a = self._hot_args = self._args(x, indices, weights, out, scale_mode)
             self._hot_ref = C.byref(a)
-            self._stream_of = torch.cuda.current_stream
+            self._dev_index = x.device.index if x.device.index is not None else torch.cuda.current_device()
         else:
             a.num_tokens = x.shape[0]
             a.x, a.indices, a.weights, a.out = x.data_ptr(), indices.data_ptr(), weights.data_ptr(), out.data_ptr()
             a.epoch, a.scale_mode = self.epoch, scale_mode
             a.trace = self._trace.data_ptr() if self._trace is not None else None
-        st = self._stream_of(x.device).cuda_stream
+        st = torch._C._cuda_getCurrentRawStream(self._dev_index)  # the raw handle, without building a Stream object
         lib = self._lib
         if self._fused:
             code = lib.kb_a2a_round_trip(self._hot_ref, st)
