@@ -66,10 +66,10 @@ class ClockSampler(threading.Thread):
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index: int, period_s: float = 0.05):
+    def __init__(self, index: int, period_s: float = 0.005):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.power, self.reasons, self.max_mhz = [], [], set(), None
         self._stop_evt = threading.Event()
         try:
             import pynvml
@@ -87,6 +87,7 @@ class ClockSampler(threading.Thread):
         while not self._stop_evt.is_set():
             try:
                 self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                self.power.append(self.nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
                 mask = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
                 for bit, name in self.REASONS.items():
                     if mask & bit:
@@ -99,8 +100,12 @@ class ClockSampler(threading.Thread):
         self._stop_evt.set()
         self.join(timeout=2)
         s = sorted(self.samples)
-        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(s)}
+        # "under load": the samples taken while the board drew more than half of its peak draw in this window
+        peak = max(self.power) if self.power else 0.0
+        loaded = sorted(c for c, w in zip(self.samples, self.power) if w >= 0.5 * peak) if peak > 0 else s
+        return {"sm_mhz": loaded[len(loaded) // 2] if loaded else (s[len(s) // 2] if s else None),
+                "sm_mhz_all_samples_median": s[len(s) // 2] if s else None, "sm_mhz_min": s[0] if s else None,
+                "sm_max_mhz": self.max_mhz, "power_w_max": round(peak, 1), "reasons": sorted(self.reasons), "samples": len(s)}
 
 
 # ---------------------------------------------------------------- plumbing ----
