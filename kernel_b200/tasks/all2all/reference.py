@@ -12,9 +12,10 @@ selectable:
 * the benchmark options give a fixed token count, softmax weights and a
   per-expert scale ``(expert_id + 1) / num_experts``.
 
-Three oracles are provided: ``ref_kernel`` (collective, vectorised),
-``ref_kernel_loop`` (collective, the reference's row-by-row algorithm, for tiny
-cases) and ``ref_closed_form`` (no communication at all).
+Oracles: ``ref_kernel`` (collective, vectorised), ``ref_kernel_two_step`` (through the
+``PyTorchAllToAll`` dispatch/combine class with the reference's expert-major
+buffers), ``ref_kernel_loop`` (collective, the reference's row-by-row algorithm,
+for tiny cases) and ``ref_closed_form`` (no communication at all).
 """
 from __future__ import annotations
 
@@ -123,6 +124,92 @@ def ref_kernel(data: input_t) -> output_t:
     contrib[order] = back
     out = (contrib.float() * rd.weights.reshape(-1, 1)).view(T, k, H).sum(1)
     return out.to(cfg.out_dtype)
+
+
+class PyTorchAllToAll:
+    """Dispatch and combine as two collective steps with the reference's
+    interface (``PyTorchAllToAll``, reference.py:54-234): ``dispatch`` returns the
+    expert-major padded buffers ``(expert_num_tokens [E_local], expert_x [E_local,
+    max_recv, H], expert_meta [E_local, max_recv, META_DIM])`` and ``combine``
+    accumulates ``weights[token, k] * expert_y`` into ``out_tokens``.  Vectorised
+    (no per-row host round trips) and device/backend agnostic."""
+
+    META_DIM = 5  # global expert, source rank, source token, source k, pad
+
+    def __init__(self, cfg: MoEConfig, rank: int, world_size: int):
+        self.cfg, self.rank, self.world_size = cfg, rank, world_size
+        self.num_local_experts = cfg.num_experts // world_size
+        self.max_recv = cfg.max_num_tokens * world_size
+
+    def dispatch(self, dp_x: torch.Tensor, indices: torch.Tensor):
+        cfg, dev = self.cfg, dp_x.device
+        T, k = indices.shape
+        El, world = self.num_local_experts, self.world_size
+        flat_e = indices.reshape(-1).long()
+        dst = flat_e // El
+        order = torch.argsort(dst, stable=True)
+        send_counts = torch.bincount(dst, minlength=world)
+        tok = torch.arange(T, device=dev).repeat_interleave(k)
+        kk = torch.arange(k, device=dev).repeat(T)
+        meta = torch.stack([flat_e, torch.full_like(flat_e, self.rank), tok, kk, torch.zeros_like(flat_e)], dim=1)
+        send_x = dp_x[tok][order].contiguous()
+        send_m = meta[order].contiguous()
+        recv_counts = torch.empty_like(send_counts)
+        _a2a(recv_counts, send_counts, None, None)
+        rc, sc = recv_counts.tolist(), send_counts.tolist()
+        recv_x = torch.empty((sum(rc), cfg.hidden_dim), dtype=cfg.in_dtype, device=dev)
+        recv_m = torch.empty((sum(rc), self.META_DIM), dtype=torch.long, device=dev)
+        _a2a(recv_x, send_x, rc, sc)
+        _a2a(recv_m.view(-1), send_m.view(-1), [c * self.META_DIM for c in rc], [c * self.META_DIM for c in sc])
+        # expert-major placement: position of a row inside its expert = its rank among the
+        # rows of that expert in arrival order
+        local_e = recv_m[:, 0] % El
+        by_expert = torch.argsort(local_e, stable=True)
+        expert_num_tokens = torch.bincount(local_e, minlength=El).to(torch.int32)
+        starts = torch.cumsum(expert_num_tokens.long(), 0) - expert_num_tokens.long()
+        pos = torch.arange(local_e.numel(), device=dev) - starts[local_e[by_expert]]
+        expert_x = torch.zeros((El, self.max_recv, cfg.hidden_dim), dtype=cfg.in_dtype, device=dev)
+        expert_meta = torch.zeros((El, self.max_recv, self.META_DIM), dtype=torch.int32, device=dev)
+        expert_x[local_e[by_expert], pos] = recv_x[by_expert]
+        expert_meta[local_e[by_expert], pos] = recv_m[by_expert].to(torch.int32)
+        return expert_num_tokens, expert_x, expert_meta
+
+    def combine(self, out_tokens: torch.Tensor, weights: torch.Tensor, expert_meta: torch.Tensor, expert_y: torch.Tensor,
+                expert_num_tokens: torch.Tensor) -> torch.Tensor:
+        cfg, dev = self.cfg, out_tokens.device
+        El, world = self.num_local_experts, self.world_size
+        valid = torch.arange(self.max_recv, device=dev).unsqueeze(0) < expert_num_tokens.long().unsqueeze(1)  # [El, max_recv]
+        rows = expert_y[valid]                    # expert-major order
+        meta = expert_meta[valid].long()
+        dst = meta[:, 1]
+        order = torch.argsort(dst, stable=True)
+        send_counts = torch.bincount(dst, minlength=world)
+        recv_counts = torch.empty_like(send_counts)
+        _a2a(recv_counts, send_counts, None, None)
+        rc, sc = recv_counts.tolist(), send_counts.tolist()
+        recv_y = torch.empty((sum(rc), cfg.hidden_dim), dtype=cfg.out_dtype, device=dev)
+        recv_m = torch.empty((sum(rc), self.META_DIM), dtype=torch.long, device=dev)
+        _a2a(recv_y, rows[order].contiguous(), rc, sc)
+        _a2a(recv_m.view(-1), meta[order].contiguous().view(-1), [c * self.META_DIM for c in rc], [c * self.META_DIM for c in sc])
+        w = weights[recv_m[:, 2], recv_m[:, 3]].to(torch.float32).unsqueeze(1)
+        acc = torch.zeros(out_tokens.shape, dtype=torch.float32, device=dev)
+        acc.index_add_(0, recv_m[:, 2], recv_y.float() * w)
+        out_tokens += acc.to(out_tokens.dtype)
+        return out_tokens
+
+
+def ref_kernel_two_step(data: input_t) -> output_t:
+    """The oracle through ``PyTorchAllToAll.dispatch`` / ``combine`` (the structure of
+    the reference's ``ref_kernel``, reference.py:256-272)."""
+    cfg, rd, rank, world = data
+    ata = PyTorchAllToAll(cfg, rank, world)
+    expert_num, expert_x, expert_meta = ata.dispatch(rd.x, rd.indices)
+    scale = expert_scale_vector(cfg.num_experts, world, cfg.expert_scale, rd.x.device)
+    local = scale[rank * ata.num_local_experts:(rank + 1) * ata.num_local_experts].view(-1, 1, 1)
+    expert_y = (expert_x.float() * local).to(cfg.out_dtype)
+    y = torch.zeros(cfg.max_num_tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=rd.x.device)
+    ata.combine(y, rd.weights, expert_meta, expert_y, expert_num)
+    return y[: rd.num_tokens]
 
 
 def ref_closed_form(data: input_t) -> output_t:

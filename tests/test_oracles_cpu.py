@@ -53,7 +53,7 @@ def _a2a_compat(rank, world):
     owner = (rd.indices.long() // (16 // world)).float()
     expect = rd.x.float() * (rd.weights * (1 + owner)).sum(-1, keepdim=True)
     res = {}
-    for name, fn in [("oracle", R.ref_kernel), ("loop", R.ref_kernel_loop), ("closed", R.ref_closed_form),
+    for name, fn in [("oracle", R.ref_kernel), ("two_step", R.ref_kernel_two_step), ("loop", R.ref_kernel_loop), ("closed", R.ref_closed_form),
                      ("fused_cpu_path", S.custom_kernel), ("baseline", base.custom_kernel),
                      ("packed", base.custom_kernel_packed)]:
         out = fn(data)
@@ -136,3 +136,29 @@ def _ag_gemm(rank, world):
 def test_ag_gemm_gloo_world2():
     for ok, check, shape in run_ranks(_ag_gemm, 2):
         assert ok and check == (True, "") and shape == (64, 48)
+
+
+def _two_step_buffers(rank, world):
+    """dispatch returns expert-major padded buffers with consistent metadata."""
+    from kernel_b200.tasks.all2all import reference as R
+
+    data = R.generate_input(8, 2, 16, 6, 77, rank, world, dtype="fp32", fixed_tokens=True, device="cpu")
+    cfg, rd = data[0], data[1]
+    ata = R.PyTorchAllToAll(cfg, rank, world)
+    num, ex, meta = ata.dispatch(rd.x, rd.indices)
+    El = cfg.num_experts // world
+    ok = num.shape == (El,) and ex.shape == (El, cfg.max_num_tokens * world, 16) and meta.shape[-1] == R.PyTorchAllToAll.META_DIM
+    for le in range(El):
+        m = meta[le, : int(num[le])]
+        ok = ok and bool((m[:, 0] == rank * El + le).all())          # every row sits in its expert's buffer
+        ok = ok and bool(((m[:, 1] >= 0) & (m[:, 1] < world)).all())
+    import torch.distributed as dist
+    total = num.sum().long().clone()
+    dist.all_reduce(total)
+    return bool(ok), int(total)
+
+
+def test_two_step_dispatch_buffers_gloo_world2():
+    res = run_ranks(_two_step_buffers, 2)
+    assert all(ok for ok, _ in res)
+    assert res[0][1] == 2 * 6 * 2  # every (token, k) copy landed exactly once
