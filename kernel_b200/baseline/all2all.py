@@ -11,7 +11,9 @@ Two variants of the reference's algorithm:
   the integers are bit-cast into extra columns rather than converted to the
   float type, so ids above 2048 survive fp16.
 
-Both run on any backend/device (NCCL on GPUs, gloo on CPU).
+``custom_kernel_timed`` is the first variant with every step timed as a named phase
+(the reference's ``all2all/submission_timed.py``).  All run on any backend/device
+(NCCL on GPUs, gloo on CPU).
 """
 from __future__ import annotations
 
@@ -21,6 +23,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops.dispatch_combine import expert_scale_vector
+from ..utils.timing import PhaseTimer, format_summary
 
 META = 3  # src_token, src_k, global_expert
 
@@ -61,46 +64,92 @@ def _route(indices, El, world):
     return flat_e, counts, order
 
 
-def custom_kernel(data):
+def _run(data, tm: PhaseTimer):
     cfg, rd, rank, world = data
     dev = rd.x.device
     T, k, H = rd.num_tokens, cfg.experts_per_token, cfg.hidden_dim
     El = cfg.num_experts // world
     side = _SideStream(dev)
 
-    flat_e, send_counts, order = _route(rd.indices, El, world)
-    recv_counts = torch.empty_like(send_counts)
-    _a2a(recv_counts, send_counts)                               # collective 1
-    with side():
-        tok = torch.arange(T, device=dev).repeat_interleave(k)
-        kk = torch.arange(k, device=dev).repeat(T)
-        meta = torch.stack([tok, kk, flat_e], dim=1).to(torch.int32)[order].contiguous()
-        send_x = rd.x[tok][order].contiguous()
-    rc, sc = recv_counts.tolist(), send_counts.tolist()          # host sync
-    recv_x = torch.empty((sum(rc), H), dtype=cfg.in_dtype, device=dev)
-    recv_meta = torch.empty((sum(rc), META), dtype=torch.int32, device=dev)
-    _a2a(recv_x, send_x, rc, sc)                                 # collective 2
-    _a2a(recv_meta.view(-1), meta.view(-1), [c * META for c in rc], [c * META for c in sc])  # collective 3
+    with tm("dispatch_total"):
+        with tm("dispatch_count_calculation"):
+            flat_e, send_counts, order = _route(rd.indices, El, world)
+            recv_counts = torch.empty_like(send_counts)
+        with tm("dispatch_count_exchange"):
+            _a2a(recv_counts, send_counts)                               # collective 1
+        with tm("dispatch_data_preparation"), side():
+            tok = torch.arange(T, device=dev).repeat_interleave(k)
+            kk = torch.arange(k, device=dev).repeat(T)
+            meta = torch.stack([tok, kk, flat_e], dim=1).to(torch.int32)[order].contiguous()
+            send_x = rd.x[tok][order].contiguous()
+        with tm("dispatch_preparation"):
+            rc, sc = recv_counts.tolist(), send_counts.tolist()          # host sync
+            recv_x = torch.empty((sum(rc), H), dtype=cfg.in_dtype, device=dev)
+            recv_meta = torch.empty((sum(rc), META), dtype=torch.int32, device=dev)
+        with tm("dispatch_data_communication"):
+            _a2a(recv_x, send_x, rc, sc)                                 # collective 2
+        with tm("dispatch_meta_communication"):
+            _a2a(recv_meta.view(-1), meta.view(-1), [c * META for c in rc], [c * META for c in sc])  # collective 3
 
-    scale = expert_scale_vector(cfg.num_experts, world, cfg.expert_scale, dev)[recv_meta[:, 2].long()].unsqueeze(1)
-    y = (recv_x.float() * scale).to(cfg.out_dtype)
+    with tm("expert_computation"):
+        scale = expert_scale_vector(cfg.num_experts, world, cfg.expert_scale, dev)[recv_meta[:, 2].long()].unsqueeze(1)
+        y = (recv_x.float() * scale).to(cfg.out_dtype)
 
     # Combine: rows go back in the order they came, so the split sizes are the
     # dispatch's swapped; the reference re-derives them with a second count
     # exchange (collective 4), which is kept here to preserve its cost profile.
-    back_counts = torch.empty_like(recv_counts)
-    _a2a(back_counts, recv_counts)                               # collective 4
-    bc = back_counts.tolist()                                    # host sync
-    back = torch.empty((sum(bc), H), dtype=cfg.out_dtype, device=dev)
-    back_meta = torch.empty((sum(bc), META), dtype=torch.int32, device=dev)
-    _a2a(back, y, bc, rc)                                        # collective 5
-    _a2a(back_meta.view(-1), recv_meta.view(-1), [c * META for c in bc], [c * META for c in rc])  # collective 6
+    with tm("combine_total"):
+        with tm("combine_count_exchange"):
+            back_counts = torch.empty_like(recv_counts)
+            _a2a(back_counts, recv_counts)                               # collective 4
+        with tm("combine_preparation"):
+            bc = back_counts.tolist()                                    # host sync
+            back = torch.empty((sum(bc), H), dtype=cfg.out_dtype, device=dev)
+            back_meta = torch.empty((sum(bc), META), dtype=torch.int32, device=dev)
+        with tm("combine_data_communication"):
+            _a2a(back, y, bc, rc)                                        # collective 5
+        with tm("combine_meta_communication"):
+            _a2a(back_meta.view(-1), recv_meta.view(-1), [c * META for c in bc], [c * META for c in rc])  # collective 6
+        with tm("combine_aggregation"):
+            src_tok = back_meta[:, 0].long()
+            w = rd.weights[src_tok, back_meta[:, 1].long()].unsqueeze(1)
+            out = torch.zeros((cfg.max_num_tokens, H), dtype=torch.float32, device=dev)
+            out.scatter_add_(0, src_tok.unsqueeze(1).expand(-1, H), back.float() * w)
+            res = out.to(cfg.out_dtype)[:T]
+    return res
 
-    src_tok = back_meta[:, 0].long()
-    w = rd.weights[src_tok, back_meta[:, 1].long()].unsqueeze(1)
-    out = torch.zeros((cfg.max_num_tokens, H), dtype=torch.float32, device=dev)
-    out.scatter_add_(0, src_tok.unsqueeze(1).expand(-1, H), back.float() * w)
-    return out.to(cfg.out_dtype)[:T]
+
+_OFF = PhaseTimer(enabled=False)
+_timers: dict = {}  # device -> PhaseTimer of custom_kernel_timed
+
+
+def custom_kernel(data):
+    return _run(data, _OFF)
+
+
+def custom_kernel_timed(data):
+    """``custom_kernel`` with every step bracketed by a named phase (the phases of
+    the reference's ``all2all/submission_timed.py:46-222``).  The numbers
+    accumulate per device across calls; read them with ``timing_summary()``."""
+    dev = data[1].x.device
+    tm = _timers.get(dev)
+    if tm is None:
+        tm = _timers[dev] = PhaseTimer(dev)
+    return _run(data, tm)
+
+
+def timing_summary(device=None, reset: bool = False, rank: int = 0, echo: bool = False) -> dict:
+    """Per-phase statistics (ms) gathered by ``custom_kernel_timed`` on ``device``
+    (the only one in use if omitted); ``echo`` prints the formatted table."""
+    if not _timers:
+        return {}
+    tm = _timers[torch.device(device)] if device is not None else next(iter(_timers.values()))
+    s = tm.summary()
+    if echo:
+        print(format_summary(tm, rank), flush=True)
+    if reset:
+        tm.reset()
+    return s
 
 
 def custom_kernel_packed(data):
