@@ -6,6 +6,6 @@ reduce-scatter on the way out) and the expert-parallel MoE layer (dispatch,
 expert MLPs, combine).
 """
 from .moe import MoELayer
-from .tp_mlp import SequenceParallelMLP
+from .tp_mlp import SequenceParallelMLP, TrainableSequenceParallelMLP
 
-__all__ = ["MoELayer", "SequenceParallelMLP"]
+__all__ = ["MoELayer", "SequenceParallelMLP", "TrainableSequenceParallelMLP"]

@@ -65,3 +65,35 @@ class SequenceParallelMLP:
         for ctx in (self.up, self.down):
             if ctx.heap is not None:
                 ctx.heap.close()
+
+
+class TrainableSequenceParallelMLP(torch.nn.Module):
+    """The same block as ``SequenceParallelMLP`` with parameters and a backward
+    pass: ``ColumnParallelLinear`` (all-gather fused forward, reduce-scatter fused
+    input gradient) -> activation -> ``RowParallelLinear`` (the mirror image).
+    ``ffn_local`` is this rank's share of the MLP's hidden dimension."""
+
+    def __init__(self, tokens: int, hidden: int, ffn_local: int, bias: bool = True, activation: str = "gelu", group=None,
+                 device: Optional[torch.device] = None):
+        super().__init__()
+        from ..ops.autograd import ColumnParallelLinear, RowParallelLinear
+
+        self.up = ColumnParallelLinear(tokens, hidden, ffn_local, bias=bias, group=group, device=device)
+        self.down = RowParallelLinear(tokens, ffn_local, hidden, bias=bias, group=group, device=device)
+        self.activation = activation
+
+    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        h = self.up(x_local)
+        if self.activation == "gelu":
+            h = torch.nn.functional.gelu(h, approximate="tanh")
+        elif self.activation == "relu":
+            h = torch.relu(h)
+        elif self.activation == "silu":
+            h = torch.nn.functional.silu(h)
+        else:
+            raise ValueError(f"unknown activation {self.activation!r}")
+        return self.down(h)
+
+    def close(self) -> None:
+        self.up.close()
+        self.down.close()

@@ -43,3 +43,46 @@ def test_moe_layer_world1():
     cpu_layer_ok = torch.allclose(y.float().cpu(), ref.float(), rtol=3e-2, atol=3e-2)
     assert cpu_layer_ok, (y.float().cpu() - ref.float()).abs().max()
     layer.close()
+
+
+def _dense_grads(x_full, w1_full, b1_full, w2_full, b2, g_full):
+    leaves = [t.detach().float().requires_grad_(True) for t in (x_full, w1_full, b1_full, w2_full, b2)]
+    x, w1, b1, w2, bb2 = leaves
+    y = torch.nn.functional.silu(x @ w1.t() + b1) @ w2.t() + bb2
+    (y * g_full.float()).sum().backward()
+    return y.detach(), [t.grad for t in leaves]
+
+
+def _rel_err(a, b):
+    return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-6)
+
+
+def test_trainable_mlp_forward_backward_world1():
+    """Forward and backward of the sequence-parallel MLP on one GPU: every GEMM of
+    both passes is the tcgen05 kernel (fused front-ends at world 1, plain GEMM for
+    the weight gradients); compared with dense fp32 autograd."""
+    from kernel_b200.models import TrainableSequenceParallelMLP
+    from kernel_b200.ops import gemm as G
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(3)
+    tokens, hidden, ffn = 256, 512, 768
+    mlp = TrainableSequenceParallelMLP(tokens, hidden, ffn, activation="silu", device=dev)
+    with torch.no_grad():
+        mlp.up.bias.normal_(std=0.05)
+        mlp.down.bias.normal_(std=0.05)
+    x = torch.randn(tokens, hidden, device=dev).to(torch.bfloat16).requires_grad_(True)
+    g = torch.randn(tokens, hidden, device=dev).to(torch.bfloat16)
+    before = G.launch_count
+    y = mlp(x)
+    (y.float() * g.float()).sum().backward()
+    torch.cuda.synchronize()
+    assert G.launch_count - before >= 6  # 2 forward, 2 input-gradient, 2 weight-gradient GEMMs (+ one-off tuning launches)
+    y_ref, (dx, dw1, db1, dw2, db2) = _dense_grads(x, mlp.up.weight, mlp.up.bias, mlp.down.weight, mlp.down.bias, g)
+    assert _rel_err(y, y_ref) < 3e-2
+    assert _rel_err(x.grad, dx) < 4e-2
+    assert _rel_err(mlp.up.weight.grad, dw1) < 4e-2
+    assert _rel_err(mlp.up.bias.grad, db1) < 4e-2
+    assert _rel_err(mlp.down.weight.grad, dw2) < 4e-2
+    assert _rel_err(mlp.down.bias.grad, db2) < 4e-2
+    mlp.close()

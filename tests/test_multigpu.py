@@ -123,6 +123,66 @@ def test_ag_gemm_shapes():
             assert repeat
 
 
+def _mlp_backward(rank, world):
+    """Forward + backward of the trainable sequence-parallel MLP; returns the
+    relative errors against dense fp32 autograd on the gathered problem."""
+    import torch
+    import torch.distributed as dist
+
+    from kernel_b200.models import TrainableSequenceParallelMLP
+
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(11)  # identical full tensors on every rank
+    tokens, hidden, fl = 128 * world, 512, 256
+    ffn, tl = fl * world, 128
+    x_full = torch.randn(tokens, hidden, device=dev).to(torch.bfloat16)
+    w1_full = (torch.randn(ffn, hidden, device=dev) / hidden ** 0.5).to(torch.bfloat16)
+    b1_full = (torch.randn(ffn, device=dev) * 0.05).to(torch.bfloat16)
+    w2_full = (torch.randn(hidden, ffn, device=dev) / ffn ** 0.5).to(torch.bfloat16)
+    b2 = (torch.randn(hidden, device=dev) * 0.05).to(torch.bfloat16)
+    g_full = torch.randn(tokens, hidden, device=dev).to(torch.bfloat16)
+    mlp = TrainableSequenceParallelMLP(tokens, hidden, fl, activation="silu", device=dev)
+    with torch.no_grad():
+        mlp.up.weight.copy_(w1_full[rank * fl:(rank + 1) * fl])
+        mlp.up.bias.copy_(b1_full[rank * fl:(rank + 1) * fl])
+        mlp.down.weight.copy_(w2_full[:, rank * fl:(rank + 1) * fl])
+        mlp.down.bias.copy_(b2)
+    x_local = x_full[rank * tl:(rank + 1) * tl].clone().requires_grad_(True)
+    y_local = mlp(x_local)
+    (y_local.float() * g_full[rank * tl:(rank + 1) * tl].float()).sum().backward()
+    torch.cuda.synchronize()
+    for lin in (mlp.up, mlp.down):
+        for c in (lin.fwd, lin.bwd):
+            c.heap.check_status()
+    leaves = [t.detach().float().requires_grad_(True) for t in (x_full, w1_full, b1_full, w2_full, b2)]
+    x, w1, b1, w2, bb2 = leaves
+    y_ref = torch.nn.functional.silu(x @ w1.t() + b1) @ w2.t() + bb2
+    (y_ref * g_full.float()).sum().backward()
+    db2 = mlp.down.bias.grad.float().clone()
+    dist.all_reduce(db2)
+
+    def err(a, b):
+        return (a.float() - b).abs().max().item() / (b.abs().max().item() + 1e-6)
+
+    res = {
+        "y": err(y_local, y_ref[rank * tl:(rank + 1) * tl].detach()),
+        "dx": err(x_local.grad, x.grad[rank * tl:(rank + 1) * tl]),
+        "dw1": err(mlp.up.weight.grad, w1.grad[rank * fl:(rank + 1) * fl]),
+        "db1": err(mlp.up.bias.grad, b1.grad[rank * fl:(rank + 1) * fl]),
+        "dw2": err(mlp.down.weight.grad, w2.grad[:, rank * fl:(rank + 1) * fl]),
+        "db2": err(db2, bb2.grad),
+    }
+    dist.barrier()
+    mlp.close()
+    return res
+
+
+def test_trainable_mlp_backward_across_gpus():
+    world = _world()
+    for errs in run_ranks(_mlp_backward, world, backend="nccl", timeout=300):
+        assert max(errs.values()) < 5e-2, errs
+
+
 def _rank_leaves(rank, world):
     """A rank leaves between steps (nothing in flight); the others learn of it
     from the host-side store before their next launch."""
