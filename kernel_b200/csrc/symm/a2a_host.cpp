@@ -18,6 +18,8 @@
 #include <atomic>
 #include <vector>
 
+#include <cuda_fp16.h>  // host-callable fp16 <-> fp32 conversions
+
 #include "../common/host_util.h"
 #include "../include/kb200.h"
 
@@ -41,6 +43,15 @@ inline uint16_t f32_to_bf16(float f) {  // round to nearest even
   if ((u & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>((u >> 16) | 0x40);  // NaN stays NaN
   u += 0x7fffu + ((u >> 16) & 1u);
   return static_cast<uint16_t>(u >> 16);
+}
+
+inline float f16_to_f32(uint16_t h) {
+  __half_raw r;
+  r.x = h;
+  return __half2float(__half(r));
+}
+inline uint16_t f32_to_f16(float f) {  // round to nearest even
+  return static_cast<__half_raw>(__float2half_rn(f)).x;
 }
 
 struct Layout {
@@ -85,6 +96,10 @@ void scale_row(const Layout& L, const uint8_t* src, uint8_t* dst, float scale) {
     const float* s = reinterpret_cast<const float*>(src);
     float* d = reinterpret_cast<float*>(dst);
     for (int i = 0; i < L.H; ++i) d[i] = s[i] * scale;
+  } else if (L.dtype == 1) {
+    const uint16_t* s = reinterpret_cast<const uint16_t*>(src);
+    uint16_t* d = reinterpret_cast<uint16_t*>(dst);
+    for (int i = 0; i < L.H; ++i) d[i] = f32_to_f16(f16_to_f32(s[i]) * scale);
   } else {
     const uint16_t* s = reinterpret_cast<const uint16_t*>(src);
     uint16_t* d = reinterpret_cast<uint16_t*>(dst);
@@ -96,14 +111,14 @@ void scale_row(const Layout& L, const uint8_t* src, uint8_t* dst, float scale) {
 
 // Same arguments as the device entry points; `a->peer_base` are host pointers of
 // a KB_BACKEND_HOST heap, `a->slots` host scratch, x / indices / weights / out
-// host tensors.  dtype 0 (bf16) and 2 (fp32) are supported.
+// host tensors.  dtype 0 (bf16), 1 (fp16) and 2 (fp32).
 extern "C" int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms) {
   if (a == nullptr || a->world < 1 || a->world > KB_MAX_WORLD || a->rank < 0 || a->rank >= a->world) {
     kb::set_error("a2a host: bad rank/world");
     return KB_ERR_ARG;
   }
-  if (a->dtype != 0 && a->dtype != 2) {
-    kb::set_error("a2a host: dtype %d not supported on the host path (bf16 and fp32 are)", a->dtype);
+  if (a->dtype < 0 || a->dtype > 2) {
+    kb::set_error("a2a host: dtype %d not supported on the host path (bf16, fp16 and fp32 are)", a->dtype);
     return KB_ERR_ARG;
   }
   if (a->num_experts <= 0 || a->num_experts % a->world != 0 || a->num_tokens < 0 || a->num_tokens > a->max_tokens) {
@@ -192,6 +207,9 @@ extern "C" int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms) {
       if (L.dtype == 2) {
         const float* r = reinterpret_cast<const float*>(row);
         for (int i = 0; i < L.H; ++i) acc[i] += w * r[i];
+      } else if (L.dtype == 1) {
+        const uint16_t* r = reinterpret_cast<const uint16_t*>(row);
+        for (int i = 0; i < L.H; ++i) acc[i] += w * f16_to_f32(r[i]);
       } else {
         const uint16_t* r = reinterpret_cast<const uint16_t*>(row);
         for (int i = 0; i < L.H; ++i) acc[i] += w * bf16_to_f32(r[i]);
@@ -199,6 +217,9 @@ extern "C" int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms) {
     }
     if (L.dtype == 2) {
       memcpy(out + static_cast<size_t>(t) * L.row_bytes, acc.data(), L.row_bytes);
+    } else if (L.dtype == 1) {
+      uint16_t* o = reinterpret_cast<uint16_t*>(out + static_cast<size_t>(t) * L.row_bytes);
+      for (int i = 0; i < L.H; ++i) o[i] = f32_to_f16(acc[i]);
     } else {
       uint16_t* o = reinterpret_cast<uint16_t*>(out + static_cast<size_t>(t) * L.row_bytes);
       for (int i = 0; i < L.H; ++i) o[i] = f32_to_bf16(acc[i]);

@@ -58,9 +58,9 @@ class MoEAllToAll:
         self.epoch = 0
         self.heap = None
         self._trace = None
-        # CPU ranks: the same protocol over a memfd-backed symmetric heap (bf16 and
+        # CPU ranks: the same protocol over a memfd-backed symmetric heap (bf16, fp16,
         # fp32), or torch.distributed collectives (any dtype; KB200_A2A_CPU_PATH=collectives).
-        self.host_heap = (not self.native and dtype in (torch.bfloat16, torch.float32)
+        self.host_heap = (not self.native and dtype in _DTYPES
                           and os.environ.get("KB200_A2A_CPU_PATH", "heap") == "heap")
         if self.native or self.host_heap:
             if dtype not in _DTYPES:
