@@ -109,6 +109,9 @@ typedef struct KbGemmArgs {
 } KbGemmArgs;
 
 int kb_gemm(const KbGemmArgs* args, void* stream);
+// The fused modes (RS, AG) run by a CPU rank over a KB_BACKEND_HOST heap: same
+// schedule, staging layouts, flags and rounding points as the kernel (symm/gemm_host.cpp).
+int kb_gemm_host(const KbGemmArgs* args, int timeout_ms);
 // Host replica of the kernel's static tile schedule (tests of the index arithmetic).
 int kb_gemm_schedule(int mode, int M, int N, int rank, int world, int pair, int pos, int* block, int* nb);
 // Bytes each rank needs in the symmetric heap for the given problem.

@@ -4,7 +4,8 @@ all-gather + GEMM.
 On CUDA tensors these always launch the hand-written sm_100a kernel
 (``csrc/kernels/gemm_sm100.cu``); there is no library fallback on a GPU.  CPU
 tensors take a torch reference path (``torch.matmul`` plus gloo collectives) so
-that host-side logic can be tested without a GPU.
+that host-side logic can be tested without a GPU; with more than one CPU rank the
+fused ops run the kernels' protocol over a host-backed symmetric heap.
 
 Counterparts in the reference: ``gemm_rs/submission.py:5-29`` (matmul, bias add,
 ``reduce_scatter_tensor``).  The all-gather variant has no counterpart there.
@@ -38,6 +39,38 @@ def _launch(args: N.GemmArgs, device: torch.device) -> None:
     if code:
         N.check(code)
     launch_count += 1
+
+
+def _cpu_heap_path() -> bool:
+    """CPU ranks run the kernels' protocol over a memfd-backed symmetric heap
+    (``csrc/symm/gemm_host.cpp``) unless ``KB200_GEMM_CPU_PATH=collectives`` selects
+    torch matmul + gloo collectives."""
+    return os.environ.get("KB200_GEMM_CPU_PATH", "heap") == "heap"
+
+
+def _new_heap(nbytes: int, group, device, native: bool) -> SymmHeap:
+    if native:
+        return SymmHeap(nbytes, group=group, device=device)
+    return SymmHeap(nbytes, group=group, backend="host", timeout_s=_WAIT_LIMIT_NS / 1e9 + 5)
+
+
+def _host_args(ctx, mode: int, M: int, Nn: int, K: int, a, w, bias, bias_scale: float, out) -> N.GemmArgs:
+    args = N.GemmArgs()
+    args.mode = mode
+    args.M, args.N, args.K = M, Nn, K
+    args.A, args.B, args.out = a.data_ptr(), w.data_ptr(), out.data_ptr()
+    args.bias = bias.data_ptr() if bias is not None else None
+    args.bias_scale = bias_scale
+    args.rank, args.world, args.epoch = ctx.rank, ctx.world, ctx.epoch
+    args.peer_base = ctx.heap.peer_array()
+    args.data_off, args.flag_off = ctx.data_off, ctx.flag_off
+    args.wait_limit_ns = _WAIT_LIMIT_NS
+    return args
+
+
+def _rows_bad(rpo: int) -> bool:
+    """The tile schedule needs the rows per rank to divide, or be a multiple of, the 128-row block."""
+    return rpo <= 0 or (rpo % 128 != 0 and 128 % rpo != 0)
 
 
 _NO_PAIR_BIT = 1 << 30
@@ -140,11 +173,12 @@ class GemmRS:
         self.epoch = 0
         self.heap = None
         self._hot = None
-        if self.native and self.world > 1:
+        self.host_heap = not self.native and self.world > 1 and _cpu_heap_path() and not _rows_bad(M // self.world)
+        if (self.native and self.world > 1) or self.host_heap:
             lib = N.lib()
             data = int(lib.kb_gemm_rs_data_bytes(M, Nn, self.world))
             flags = int(lib.kb_gemm_rs_flag_bytes(M, Nn, self.world))
-            self.heap = heap or SymmHeap(data + flags + 1024, group=group, device=device)
+            self.heap = heap or _new_heap(data + flags + 1024, group, device, self.native)
             self.data_off = self.heap.alloc(data)
             self.flag_off = self.heap.alloc(flags)
             self.status = self.heap.status
@@ -159,6 +193,13 @@ class GemmRS:
         if M != self.M or w.shape[0] != self.N or w.shape[1] != K:
             raise ValueError("shape does not match this GemmRS context")
         rows = M // self.world
+        if not a.is_cuda and self.host_heap:
+            if out is None:
+                out = torch.empty((rows, self.N), dtype=torch.bfloat16)
+            self.epoch += 1
+            args = _host_args(self, N.GEMM_RS, M, self.N, K, a, w, bias, bias_scale, out)
+            N.check(N.lib().kb_gemm_host(C.byref(args), max(1, _WAIT_LIMIT_NS // 1_000_000)))
+            return out
         if not a.is_cuda:
             full = a.float() @ w.float().t()
             full = full.to(torch.bfloat16)
@@ -216,12 +257,13 @@ class AGGemm:
         self.epoch = 0
         self.heap = None
         self._hot = None
-        if self.native and self.world > 1:
+        self.host_heap = not self.native and self.world > 1 and _cpu_heap_path() and not _rows_bad(M // self.world)
+        if (self.native and self.world > 1) or self.host_heap:
             lib = N.lib()
             data = int(lib.kb_gemm_ag_data_bytes(M, K))
             flags = int(lib.kb_gemm_ag_flag_bytes(M, self.world))
             ctr = int(lib.kb_gemm_ag_counter_bytes(M, self.world))
-            self.heap = heap or SymmHeap(data + flags + ctr + 2048, group=group, device=device)
+            self.heap = heap or _new_heap(data + flags + ctr + 2048, group, device, self.native)
             self.data_off = self.heap.alloc(data)
             self.flag_off = self.heap.alloc(flags)
             self.counter_off = self.heap.alloc(ctr)
@@ -237,6 +279,13 @@ class AGGemm:
         if rows * self.world != self.M or K != self.K or w.shape[1] != K:
             raise ValueError("shape does not match this AGGemm context")
         Nl = w.shape[0]
+        if not a_local.is_cuda and self.host_heap:
+            if out is None:
+                out = torch.empty((self.M, Nl), dtype=torch.bfloat16)
+            self.epoch += 1
+            args = _host_args(self, N.GEMM_AG, self.M, Nl, K, a_local, w, bias, 1.0, out)
+            N.check(N.lib().kb_gemm_host(C.byref(args), max(1, _WAIT_LIMIT_NS // 1_000_000)))
+            return out
         if not a_local.is_cuda:
             full = torch.empty((self.M, K), dtype=a_local.dtype)
             if self.world > 1:
