@@ -152,9 +152,12 @@ int kb_a2a_dispatch(const KbA2aArgs* a, void* stream);
 int kb_a2a_expert_scale(const KbA2aArgs* a, void* stream);
 int kb_a2a_combine(const KbA2aArgs* a, void* stream);
 // The same round trip executed by a CPU rank over a KB_BACKEND_HOST heap (all
-// pointers are host pointers; bf16 and fp32).  Returns KB_ERR_TIMEOUT naming the
-// rank that never arrived.
+// pointers are host pointers; bf16, fp16 and fp32).  Returns KB_ERR_TIMEOUT naming
+// the rank that never arrived.  The dispatch and combine phases are also callable
+// on their own, around an expert computation of the caller.
 int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms);
+int kb_a2a_dispatch_host(const KbA2aArgs* a, int timeout_ms);
+int kb_a2a_combine_host(const KbA2aArgs* a, int timeout_ms);
 // dispatch + simulated expert + combine in ONE cooperative launch.
 int kb_a2a_round_trip(const KbA2aArgs* a, void* stream);
 

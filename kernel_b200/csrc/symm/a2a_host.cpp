@@ -107,12 +107,7 @@ void scale_row(const Layout& L, const uint8_t* src, uint8_t* dst, float scale) {
   }
 }
 
-}  // namespace
-
-// Same arguments as the device entry points; `a->peer_base` are host pointers of
-// a KB_BACKEND_HOST heap, `a->slots` host scratch, x / indices / weights / out
-// host tensors.  dtype 0 (bf16), 1 (fp16) and 2 (fp32).
-extern "C" int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms) {
+int make_layout(const KbA2aArgs* a, Layout& L) {
   if (a == nullptr || a->world < 1 || a->world > KB_MAX_WORLD || a->rank < 0 || a->rank >= a->world) {
     kb::set_error("a2a host: bad rank/world");
     return KB_ERR_ARG;
@@ -125,7 +120,6 @@ extern "C" int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms) {
     kb::set_error("a2a host: bad expert or token count");
     return KB_ERR_ARG;
   }
-  Layout L;
   L.rank = a->rank;
   L.world = a->world;
   L.E = a->num_experts;
@@ -148,12 +142,17 @@ extern "C" int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms) {
   L.y_off = a->y_off;
   L.count_off = a->count_off;
   L.flag_off = a->flag_off;
-  const int64_t deadline = now_ms() + (timeout_ms > 0 ? timeout_ms : 30000);
-  const uint8_t* x = static_cast<const uint8_t*>(a->x);
-  uint8_t* out = static_cast<uint8_t*>(a->out);
+  return KB_OK;
+}
 
-  // ---- dispatch: slot of entry i = first slot of its expert in the owner's
-  // region for this source + number of earlier entries with the same expert.
+int64_t deadline_of(int timeout_ms) { return now_ms() + (timeout_ms > 0 ? timeout_ms : 30000); }
+
+// Slot of entry i = first slot of its expert in the owner's region for this
+// source + number of earlier entries with the same expert.  Rows and counts go
+// straight into the owners' segments, then the dispatch flag; returns once every
+// source's rows have arrived here.
+int dispatch_phase(const KbA2aArgs* a, const Layout& L, int64_t deadline) {
+  const uint8_t* x = static_cast<const uint8_t*>(a->x);
   std::vector<int> tot(L.E, 0), off(L.E, 0), seen(L.E, 0);
   const int n = L.T * L.k;
   for (int i = 0; i < n; ++i) {
@@ -177,10 +176,11 @@ extern "C" int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms) {
   }
   for (int e = 0; e < L.E; ++e) L.counts(e / L.El, L.rank)[e % L.El] = tot[e];
   for (int r = 0; r < L.world; ++r) L.flag(r, 0, L.rank)->store(a->epoch, std::memory_order_release);
+  return wait_all(L, 0, a->epoch, deadline, "its dispatch");
+}
 
-  // ---- expert: y = scale(expert) * x for every received row
-  int rc = wait_all(L, 0, a->epoch, deadline, "its dispatch");
-  if (rc != KB_OK) return rc;
+// y = scale(expert) * x for every received row.
+void expert_phase(const KbA2aArgs* a, const Layout& L) {
   for (int s = 0; s < L.world; ++s) {
     int row = 0;
     for (int le = 0; le < L.El; ++le) {
@@ -192,10 +192,14 @@ extern "C" int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms) {
       }
     }
   }
-  for (int r = 0; r < L.world; ++r) L.flag(r, 1, L.rank)->store(a->epoch, std::memory_order_release);
+}
 
-  // ---- combine: pull the k rows of every token, fp32 sum in k order
-  rc = wait_all(L, 1, a->epoch, deadline, "its expert pass");
+// Publishes this rank's expert outputs, waits for everybody's, then pulls the k
+// rows of every token and sums them in fp32 in k order.
+int combine_phase(const KbA2aArgs* a, const Layout& L, int64_t deadline) {
+  uint8_t* out = static_cast<uint8_t*>(a->out);
+  for (int r = 0; r < L.world; ++r) L.flag(r, 1, L.rank)->store(a->epoch, std::memory_order_release);
+  const int rc = wait_all(L, 1, a->epoch, deadline, "its expert pass");
   if (rc != KB_OK) return rc;
   std::vector<float> acc(L.H);
   for (int t = 0; t < L.T; ++t) {
@@ -226,4 +230,43 @@ extern "C" int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms) {
     }
   }
   return KB_OK;
+}
+
+}  // namespace
+
+// Same arguments as the device entry points; `a->peer_base` are host pointers of
+// a KB_BACKEND_HOST heap, `a->slots` host scratch, x / indices / weights / out
+// host tensors.  dtype 0 (bf16), 1 (fp16) and 2 (fp32).
+extern "C" int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms) {
+  Layout L;
+  int rc = make_layout(a, L);
+  if (rc != KB_OK) return rc;
+  const int64_t deadline = deadline_of(timeout_ms);
+  rc = dispatch_phase(a, L, deadline);
+  if (rc != KB_OK) return rc;
+  expert_phase(a, L);
+  return combine_phase(a, L, deadline);
+}
+
+// The phases on their own, for callers that run their own expert computation
+// between them: after kb_a2a_dispatch_host the receive region and the counts of
+// this rank are complete; kb_a2a_combine_host expects the expert outputs in the
+// y region, row for row, and uses the slots the dispatch of the same epoch left
+// in `a->slots`.
+extern "C" int kb_a2a_dispatch_host(const KbA2aArgs* a, int timeout_ms) {
+  Layout L;
+  const int rc = make_layout(a, L);
+  if (rc != KB_OK) return rc;
+  return dispatch_phase(a, L, deadline_of(timeout_ms));
+}
+
+extern "C" int kb_a2a_combine_host(const KbA2aArgs* a, int timeout_ms) {
+  Layout L;
+  const int rc = make_layout(a, L);
+  if (rc != KB_OK) return rc;
+  if (a->out == nullptr || a->weights == nullptr) {
+    kb::set_error("a2a host: combine needs weights and an output");
+    return KB_ERR_ARG;
+  }
+  return combine_phase(a, L, deadline_of(timeout_ms));
 }

@@ -5,7 +5,7 @@ transformer: the sequence-parallel MLP (all-gather + GEMM on the way in, GEMM +
 reduce-scatter on the way out) and the expert-parallel MoE layer (dispatch,
 expert MLPs, combine).
 """
-from .moe import MoELayer
+from .moe import MoELayer, TrainableMoELayer
 from .tp_mlp import SequenceParallelMLP, TrainableSequenceParallelMLP
 
-__all__ = ["MoELayer", "SequenceParallelMLP", "TrainableSequenceParallelMLP"]
+__all__ = ["MoELayer", "TrainableMoELayer", "SequenceParallelMLP", "TrainableSequenceParallelMLP"]

@@ -192,7 +192,14 @@ class MoEAllToAll:
         """
         self._validate(x, indices, None)
         if not x.is_cuda:
-            raise RuntimeError("split dispatch/combine needs the CUDA path; use dispatch_scale_combine on CPU")
+            if not self.host_heap:
+                raise RuntimeError("split dispatch/combine on CPU needs the host-heap path (KB200_A2A_CPU_PATH=heap)")
+            self.epoch += 1
+            a = self._args(x, indices, None, None, SCALE_IDENTITY)
+            N.check(self._lib.kb_a2a_dispatch_host(C.byref(a), max(1, _WAIT_LIMIT_NS // 1_000_000)))
+            counts = self.heap.tensor(self.count_off, (self.world, self.El), torch.int32)
+            recv = self.heap.tensor(self.recv_off, (self.world, self.cap, self.H), self.dtype)
+            return counts, recv
         global launch_count
         self.epoch += 1
         a = self._args(x, indices, None, None, SCALE_IDENTITY)
@@ -217,6 +224,11 @@ class MoEAllToAll:
         global launch_count
         out = torch.empty_like(x_like)
         a = self._args(x_like, indices, weights, out, SCALE_IDENTITY)
+        if not x_like.is_cuda:
+            if not self.host_heap:
+                raise RuntimeError("split dispatch/combine on CPU needs the host-heap path (KB200_A2A_CPU_PATH=heap)")
+            N.check(self._lib.kb_a2a_combine_host(C.byref(a), max(1, _WAIT_LIMIT_NS // 1_000_000)))
+            return out
         lib = N.lib()
         st = torch.cuda.current_stream(x_like.device).cuda_stream
         # y-ready flags of this epoch go out through a barrier-style post.

@@ -83,3 +83,78 @@ def test_no_weight_grad_skips_gather():
     assert lin.weight.grad is None and x.grad.shape == (8, 16)
     expect = lin.weight.detach().float().sum(0).expand(8, 16)
     assert torch.allclose(x.grad.float(), expect, rtol=2e-2, atol=2e-2)
+
+
+def _moe_rank(rank, world):
+    import torch.distributed as dist
+
+    from kernel_b200.models import TrainableMoELayer
+
+    E, k, H, F, T = 4 * world, 2, 32, 48, 6 + rank
+    El = E // world
+    full = torch.Generator().manual_seed(5)  # identical expert weights on every rank
+    w_up_full = (torch.randn(E, F, H, generator=full) / H ** 0.5).to(torch.bfloat16)
+    w_down_full = (torch.randn(E, H, F, generator=full) / F ** 0.5).to(torch.bfloat16)
+    layer = TrainableMoELayer(E, k, H, F, 16, device="cpu")
+    with torch.no_grad():
+        layer.w_up.copy_(w_up_full[rank * El:(rank + 1) * El])
+        layer.w_down.copy_(w_down_full[rank * El:(rank + 1) * El])
+    g = torch.Generator().manual_seed(50 + rank)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).requires_grad_(True)
+    idx = torch.rand(T, E, generator=g).argsort(1)[:, :k].to(torch.int32).contiguous()
+    w = torch.softmax(torch.randn(T, k, generator=g), -1).requires_grad_(True)
+    gy = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    for _ in range(2):  # two steps on the same workspaces
+        for t in (x, w, layer.w_up, layer.w_down):
+            t.grad = None
+        y = layer(x, idx, w)
+        (y.float() * gy.float()).sum().backward()
+
+    # dense fp32 autograd over all experts; expert gradients summed over the ranks' losses
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().clone().requires_grad_(True)
+    up = w_up_full.float().requires_grad_(True)
+    down = w_down_full.float().requires_grad_(True)
+    yr = torch.zeros(T, H)
+    for t in range(T):
+        for j in range(k):
+            e = int(idx[t, j])
+            yr[t] = yr[t] + wr[t, j] * (torch.nn.functional.silu(xr[t] @ up[e].t()) @ down[e].t())
+    (yr * gy.float()).sum().backward()
+    gup, gdown = up.grad.clone(), down.grad.clone()
+    if world > 1:
+        dist.all_reduce(gup)
+        dist.all_reduce(gdown)
+
+    def close(a, b, tol=6e-2):
+        return (a.float() - b).abs().max().item() / (b.abs().max().item() + 1e-6) < tol
+
+    res = {
+        "y": close(y, yr.detach()),
+        "dx": close(x.grad, xr.grad),
+        "dw": close(w.grad, wr.grad),
+        "dup": close(layer.w_up.grad, gup[rank * El:(rank + 1) * El]),
+        "ddown": close(layer.w_down.grad, gdown[rank * El:(rank + 1) * El]),
+    }
+    layer.close()
+    return res
+
+
+def test_trainable_moe_backward_single_process():
+    r = _moe_rank(0, 1)
+    assert all(r.values()), r
+
+
+def test_trainable_moe_backward_host_heap_world3():
+    for r in run_ranks(_moe_rank, 3):
+        assert all(r.values()), r
+
+
+def test_expert_major_rows_order():
+    from kernel_b200.models.moe import _expert_major_rows
+
+    counts = torch.tensor([[2, 0, 1], [1, 3, 0]], dtype=torch.int32)   # [world 2, El 3], capacity 10 rows per source
+    idx, n_e = _expert_major_rows(counts, 10)
+    assert n_e == [3, 3, 1]
+    # expert 0: src0 rows 0,1 and src1 row 0; expert 1: src1 rows 1..3; expert 2: src0 row 2
+    assert idx.tolist() == [0, 1, 10, 11, 12, 13, 2]

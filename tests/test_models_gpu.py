@@ -86,3 +86,40 @@ def test_trainable_mlp_forward_backward_world1():
     assert _rel_err(mlp.down.weight.grad, dw2) < 4e-2
     assert _rel_err(mlp.down.bias.grad, db2) < 4e-2
     mlp.close()
+
+
+def test_trainable_moe_forward_backward_world1():
+    """MoE block with backward on one GPU against dense fp32 autograd: the exchanges
+    are the dispatch/combine kernels (also for the gradients), the GEMMs the tcgen05 kernel."""
+    from kernel_b200.models import TrainableMoELayer
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(5)
+    E, k, H, F, T = 8, 2, 256, 384, 40
+    layer = TrainableMoELayer(E, k, H, F, 64, device=dev)
+    x = torch.randn(T, H, device=dev).to(torch.bfloat16).requires_grad_(True)
+    idx = torch.rand(T, E, device=dev).argsort(1)[:, :k].to(torch.int32).contiguous()
+    w = torch.softmax(torch.randn(T, k, device=dev), -1).requires_grad_(True)
+    gy = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    for _ in range(2):
+        for t in (x, w, layer.w_up, layer.w_down):
+            t.grad = None
+        y = layer(x, idx, w)
+        (y.float() * gy.float()).sum().backward()
+    torch.cuda.synchronize()
+    layer.a2a.heap.check_status()
+    layer.meta.heap.check_status()
+
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().clone().requires_grad_(True)
+    up = layer.w_up.detach().float().requires_grad_(True)
+    down = layer.w_down.detach().float().requires_grad_(True)
+    hid = torch.nn.functional.silu(torch.einsum("th,tkfh->tkf", xr, up[idx.long()]))
+    yr = (torch.einsum("tkf,tkhf->tkh", hid, down[idx.long()]) * wr.unsqueeze(-1)).sum(1)
+    (yr * gy.float()).sum().backward()
+    assert _rel_err(y, yr.detach()) < 3e-2
+    assert _rel_err(x.grad, xr.grad) < 5e-2
+    assert _rel_err(w.grad, wr.grad) < 5e-2
+    assert _rel_err(layer.w_up.grad, up.grad) < 5e-2
+    assert _rel_err(layer.w_down.grad, down.grad) < 5e-2
+    layer.close()

@@ -183,6 +183,66 @@ def test_trainable_mlp_backward_across_gpus():
         assert max(errs.values()) < 5e-2, errs
 
 
+def _moe_backward(rank, world):
+    """Two training steps of the expert-parallel MoE block; relative errors against
+    dense fp32 autograd over all experts (expert gradients summed over the ranks)."""
+    import torch
+    import torch.distributed as dist
+
+    from kernel_b200.models import TrainableMoELayer
+
+    dev = torch.device("cuda", rank)
+    E, k, H, F, T = 4 * world, 2, 256, 384, 24 + rank
+    El = E // world
+    full = torch.Generator(device=dev).manual_seed(5)
+    w_up_full = (torch.randn(E, F, H, device=dev, generator=full) / H ** 0.5).to(torch.bfloat16)
+    w_down_full = (torch.randn(E, H, F, device=dev, generator=full) / F ** 0.5).to(torch.bfloat16)
+    layer = TrainableMoELayer(E, k, H, F, 64, device=dev)
+    with torch.no_grad():
+        layer.w_up.copy_(w_up_full[rank * El:(rank + 1) * El])
+        layer.w_down.copy_(w_down_full[rank * El:(rank + 1) * El])
+    g = torch.Generator(device=dev).manual_seed(50 + rank)
+    x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+    idx = torch.rand(T, E, device=dev, generator=g).argsort(1)[:, :k].to(torch.int32).contiguous()
+    w = torch.softmax(torch.randn(T, k, device=dev, generator=g), -1).requires_grad_(True)
+    gy = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    for _ in range(2):
+        for t in (x, w, layer.w_up, layer.w_down):
+            t.grad = None
+        y = layer(x, idx, w)
+        (y.float() * gy.float()).sum().backward()
+    torch.cuda.synchronize()
+    layer.a2a.heap.check_status()
+    layer.meta.heap.check_status()
+
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().clone().requires_grad_(True)
+    up = w_up_full.float().requires_grad_(True)
+    down = w_down_full.float().requires_grad_(True)
+    hid = torch.nn.functional.silu(torch.einsum("th,tkfh->tkf", xr, up[idx.long()]))
+    yr = (torch.einsum("tkf,tkhf->tkh", hid, down[idx.long()]) * wr.unsqueeze(-1)).sum(1)
+    (yr * gy.float()).sum().backward()
+    gup, gdown = up.grad.clone(), down.grad.clone()
+    dist.all_reduce(gup)
+    dist.all_reduce(gdown)
+
+    def err(a, b):
+        return (a.float() - b).abs().max().item() / (b.abs().max().item() + 1e-6)
+
+    res = {"y": err(y, yr.detach()), "dx": err(x.grad, xr.grad), "dw": err(w.grad, wr.grad),
+           "dup": err(layer.w_up.grad, gup[rank * El:(rank + 1) * El]),
+           "ddown": err(layer.w_down.grad, gdown[rank * El:(rank + 1) * El])}
+    dist.barrier()
+    layer.close()
+    return res
+
+
+def test_trainable_moe_backward_across_gpus():
+    world = _world()
+    for errs in run_ranks(_moe_backward, world, backend="nccl", timeout=300):
+        assert max(errs.values()) < 5e-2, errs
+
+
 def _rank_leaves(rank, world):
     """A rank leaves between steps (nothing in flight); the others learn of it
     from the host-side store before their next launch."""
