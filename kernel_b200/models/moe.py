@@ -27,20 +27,22 @@ class MoELayer:
 
     def __call__(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         a2a = self.a2a
-        if not x.is_cuda:
+        if not x.is_cuda and not a2a.host_heap:
             return self._dense(x, indices, weights)
         counts, recv = a2a.dispatch(x, indices)
-        y = a2a.expert_output_buffer()
-        counts_h = counts.cpu()  # the segment lengths size the GEMMs (one sync per layer call)
-        for s in range(a2a.world):
-            off = 0
-            for le in range(a2a.El):
-                c = int(counts_h[s, le])
-                if c:
-                    h = gemm(recv[s, off:off + c], self.w_up[le])
-                    h = torch.nn.functional.silu(h)
-                    gemm(h, self.w_down[le], out=y[s, off:off + c])
-                off += c
+        # the segment lengths size the GEMMs (one sync per layer call); the rows of
+        # one expert, from all sources, are gathered into one block per expert
+        rows_idx, n_e = _expert_major_rows(counts.cpu(), a2a.cap)
+        rows_idx = rows_idx.to(x.device)
+        X = recv.view(-1, a2a.H)[rows_idx]
+        Y = torch.empty_like(X)
+        o = 0
+        for le, n in enumerate(n_e):
+            if n:
+                h = torch.nn.functional.silu(_gemm(X[o:o + n], self.w_up[le]))
+                gemm(h, self.w_down[le], out=Y[o:o + n], pair=False)
+            o += n
+        a2a.expert_output_buffer().view(-1, a2a.H)[rows_idx] = Y
         return a2a.combine(x, indices, weights)
 
     def _dense(self, x, indices, weights) -> torch.Tensor:

@@ -36,3 +36,37 @@ def test_moe_layer_dense_formulation_matches_manual():
             h = torch.nn.functional.silu(x[t].float() @ w_up[e].float().t())
             manual[t] += w[t, j] * (h @ w_down[e].float().t())
     assert torch.allclose(y.float(), manual, rtol=5e-2, atol=5e-2)
+
+
+def _moe_layer_ranks(rank, world):
+    """Forward of the expert-parallel layer on CPU ranks (host-heap dispatch and
+    combine around real expert MLPs) against the single-process formulation with all experts."""
+    from kernel_b200.models import MoELayer
+
+    E, k, H, F, T = 3 * world, 2, 32, 64, 5 + rank
+    El = E // world
+    full = torch.Generator().manual_seed(9)
+    w_up = (torch.randn(E, F, H, generator=full) / H ** 0.5).to(torch.bfloat16)
+    w_down = (torch.randn(E, H, F, generator=full) / F ** 0.5).to(torch.bfloat16)
+    layer = MoELayer(E, k, H, 8, w_up[rank * El:(rank + 1) * El], w_down[rank * El:(rank + 1) * El])
+    g = torch.Generator().manual_seed(20 + rank)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    idx = torch.rand(T, E, generator=g).argsort(1)[:, :k].to(torch.int32).contiguous()
+    w = torch.softmax(torch.randn(T, k, generator=g), -1)
+    y1 = layer(x, idx, w)
+    y2 = layer(x, idx, w)
+    manual = torch.zeros(T, H)
+    for t in range(T):
+        for j in range(k):
+            e = int(idx[t, j])
+            h = torch.nn.functional.silu(x[t].float() @ w_up[e].float().t())
+            manual[t] += w[t, j] * (h @ w_down[e].float().t())
+    ok = torch.allclose(y1.float(), manual, rtol=5e-2, atol=5e-2) and torch.equal(y1, y2)
+    layer.close()
+    return bool(ok)
+
+
+def test_moe_layer_on_cpu_ranks_world3():
+    from _mp import run_ranks
+
+    assert all(run_ranks(_moe_layer_ranks, 3))
