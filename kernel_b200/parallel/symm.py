@@ -81,7 +81,7 @@ class SymmHeap:
         self._h = C.c_void_p()
         self._bump = _RESERVED
         self._barrier_epoch = 0
-        self._views = []
+        self._views = {}  # host backend: (address, bytes) -> ctypes buffer kept alive for the tensors that alias it
         self.mc_ptr: Optional[int] = None
 
         session = self._broadcast_session()
@@ -207,9 +207,10 @@ class SymmHeap:
             raise ValueError("range outside the symmetric segment")
         ptr = self.peer_ptrs[peer] + offset
         if self.backend == "host":
-            buf = (C.c_char * nbytes).from_address(ptr)
+            buf = self._views.get((ptr, nbytes))
+            if buf is None:  # one buffer object per range however often it is viewed
+                buf = self._views[(ptr, nbytes)] = (C.c_char * nbytes).from_address(ptr)
             flat = torch.frombuffer(buf, dtype=torch.uint8)
-            self._views.append(buf)
         else:
             flat = torch.as_tensor(_CudaView(ptr, nbytes, self), device=self.device)
         return flat.view(dtype).view(*shape)
