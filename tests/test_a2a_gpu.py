@@ -129,3 +129,33 @@ def test_sentinel_and_guard_rows_after_dispatch():
     inside, outside = ctx.verify_workspace()
     assert inside == 0 and outside == 0
     assert torch.isfinite(out.float()).all()
+
+
+@pytest.mark.parametrize("fused", ["1", "0"])
+@pytest.mark.parametrize("E,k,T", [(2, 1, 3), (2, 2, 3), (4, 2, 2), (3, 3, 1)])
+def test_every_routing_of_tiny_cases(E, k, T, fused, monkeypatch):
+    """All ordered picks of k distinct experts for every token, one call each on the
+    same workspace (an epoch per call): no slot combination is left untested at
+    these sizes.  fp32, closed-form expectation."""
+    import itertools
+
+    from kernel_b200.ops.dispatch_combine import SCALE_EXPERT, MoEAllToAll, expert_scale_vector
+
+    monkeypatch.setenv("KB200_A2A_FUSED", fused)
+    dev = torch.device("cuda")
+    H = 64
+    ctx = MoEAllToAll(E, k, H, 4, dtype=torch.float32, device=dev)
+    per_token = list(itertools.permutations(range(E), k))
+    combos = list(itertools.product(per_token, repeat=T))
+    g = torch.Generator(device=dev).manual_seed(E * 100 + k * 10 + T)
+    x = torch.randn(T, H, device=dev, generator=g)
+    w = torch.rand(T, k, device=dev, generator=g)
+    scale = expert_scale_vector(E, 1, SCALE_EXPERT, dev)
+    all_idx = torch.tensor(combos, dtype=torch.int32, device=dev)       # [combos, T, k]
+    outs = [ctx.dispatch_scale_combine(x, all_idx[c].contiguous(), w, SCALE_EXPERT) for c in range(len(combos))]
+    torch.cuda.synchronize()
+    ctx.heap.check_status()
+    got = torch.stack(outs)
+    ref = x.unsqueeze(0) * (w.unsqueeze(0) * scale[all_idx.long()]).sum(-1, keepdim=True)
+    assert torch.allclose(got, ref, rtol=1e-5, atol=1e-6)
+    ctx.heap.close()
