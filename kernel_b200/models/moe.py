@@ -3,7 +3,9 @@
 Where the reference simulates the experts with ``x * (1 + rank)``
 (``reference.py:262``), this layer runs a real two-matrix expert MLP on the rows
 each local expert received, with the tcgen05 GEMM, and writes the results row
-for row into the buffer the combine kernel pulls from.
+for row into the buffer the combine kernel pulls from.  ``MoELayer`` is the
+forward-only block over given weights; ``TrainableMoELayer`` owns parameters and
+has a backward pass made of the same two exchange kernels.
 """
 from __future__ import annotations
 

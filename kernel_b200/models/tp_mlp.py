@@ -5,7 +5,8 @@ Activations enter and leave sharded along the token dimension.  The up
 projection is column-parallel and needs every token: all-gather fused with the
 GEMM.  The down projection is row-parallel (its K dimension is the sharded
 hidden dimension of the MLP) and produces partial sums for every token: GEMM
-fused with the reduce-scatter.  Forward only.
+fused with the reduce-scatter.  ``SequenceParallelMLP`` is the forward-only block over
+given weights; ``TrainableSequenceParallelMLP`` owns parameters and has a backward pass.
 """
 from __future__ import annotations
 

@@ -5,8 +5,10 @@
 ``dispatch_scale_combine`` round trip the all2all task measures.  On CUDA it
 launches the hand-written kernels in ``csrc/kernels/a2a.cu`` (no NCCL call, no
 host synchronisation, no allocation after construction apart from the output
-tensor).  On CPU it runs a vectorised torch implementation over
-``torch.distributed`` so that the routing logic can be tested with gloo.
+tensor).  CPU ranks run the kernels' protocol (sender-computed slots, stores into
+the owner's segment, epoch flags, pull combine) over a memfd-backed symmetric heap
+(``csrc/symm/a2a_host.cpp``), round trip or split; ``KB200_A2A_CPU_PATH=collectives``
+selects a vectorised torch implementation over ``torch.distributed`` instead.
 
 Reference counterparts: ``reference.py:54-234`` (``PyTorchAllToAll``) and
 ``submission.py:5-219`` (``OptimizedAllToAll`` / ``custom_kernel``).
