@@ -46,7 +46,7 @@ import torch
 
 from ..utils.common import clear_l2_cache, set_seed
 from .stats import Stats, calculate_stats, should_stop
-from .testcases import SpecError, TestCase, cases_from_yaml, mix_seed, parse_tests
+from .testcases import SpecError, TestCase, cases_from_yaml, parse_tests
 
 EXIT_OK, EXIT_USAGE, EXIT_NO_FD, EXIT_FAIL, EXIT_BAD_TESTS = 0, 2, 111, 112, 113
 TEST_TIMEOUT_S, BENCH_TIMEOUT_S = 120, 240

@@ -1,6 +1,5 @@
 """Bounded device-side waits: a flag that nothing sets makes the kernel give up
 after its limit and report a status; the context stays usable."""
-import ctypes as C
 import time
 
 import pytest

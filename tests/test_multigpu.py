@@ -246,8 +246,6 @@ def test_trainable_moe_backward_across_gpus():
 def _rank_leaves(rank, world):
     """A rank leaves between steps (nothing in flight); the others learn of it
     from the host-side store before their next launch."""
-    import datetime
-
     import torch
     import torch.distributed as dist
 
