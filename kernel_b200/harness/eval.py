@@ -20,7 +20,7 @@ What differs from the reference, on purpose:
   distributed tasks (per-rank table, rank 0 reported);
 * the task is a package (``--task all2all|gemm_rs|ag_gemm``; guessed from the
   case keys otherwise), the implementation is selectable (``--impl
-  fused|baseline`` or ``--submission some.module``) and the backend/device are parameters (``--backend
+  fused|baseline`` or ``--submission some.module | path/to/file.py``) and the backend/device are parameters (``--backend
   nccl|gloo``), so the same flow runs on CPU ranks;
 * a tests file may be replaced by ``--yaml <task.yml> --section tests|benchmarks``;
 * benchmark modes log, besides the reference's six keys, ``max_rank_us``,
@@ -33,6 +33,7 @@ import argparse
 import base64
 import dataclasses
 import importlib
+import importlib.util
 import json
 import multiprocessing
 import os
@@ -86,12 +87,28 @@ class RunConfig:
         elif self.impl == "baseline":
             sub = importlib.import_module(f"kernel_b200.baseline.{self.task}")
         else:
-            # any importable module with a custom_kernel(data): the role of the
-            # @SUBMISSION@ placeholder in the reference's task.yml (task.yml:2)
-            sub = importlib.import_module(self.impl)
+            # any importable module, or a .py file, with a custom_kernel(data): the role of
+            # the @SUBMISSION@ placeholder in the reference's task.yml (task.yml:2)
+            sub = load_submission(self.impl)
             if not hasattr(sub, "custom_kernel"):
                 raise ValueError(f"module {self.impl!r} has no custom_kernel")
         return ref, sub
+
+
+def load_submission(spec: str):
+    """``pkg.module`` is imported; ``path/to/file.py`` is loaded from the file (the
+    reference's evaluator imports a ``submission.py`` that sits next to it, eval.py:18)."""
+    if spec.endswith(".py") or os.sep in spec:
+        path = Path(spec).resolve()
+        if not path.is_file():
+            raise ValueError(f"submission file {spec!r} not found")
+        name = f"kb200_submission_{abs(hash(str(path))) & 0xFFFFFF:x}"
+        mod_spec = importlib.util.spec_from_file_location(name, path)
+        module = importlib.util.module_from_spec(mod_spec)
+        sys.modules[name] = module
+        mod_spec.loader.exec_module(module)
+        return module
+    return importlib.import_module(spec)
 
 
 def guess_task(args: dict) -> str:
@@ -526,7 +543,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("tests_file", nargs="?")
     ap.add_argument("--task", choices=["all2all", "gemm_rs", "ag_gemm"])
     ap.add_argument("--impl", choices=["fused", "baseline"], default="fused")
-    ap.add_argument("--submission", default=None, help="module path of a custom_kernel to evaluate instead of --impl")
+    ap.add_argument("--submission", default=None, help="module (pkg.mod) or file (path/to/file.py) with a custom_kernel to evaluate instead of --impl")
     ap.add_argument("--backend", choices=["nccl", "gloo"], default="nccl" if torch.cuda.is_available() else "gloo")
     ap.add_argument("--yaml")
     ap.add_argument("--section", default=None)

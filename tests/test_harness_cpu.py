@@ -128,3 +128,14 @@ def test_benchmark_extra_keys_baseline_and_json(tmp_path):
     assert len(rows) == 2 and rows[0]["spec"] == RS and rows[0]["speedup"] > 0
     # gemm_rs 64 x 128 x 256 on two ranks: link term 64*128*2/2 bytes at 900 GB/s
     assert abs(rows[0]["roofline_us"] - 64 * 128 * 2 / 2 / 900e9 * 1e6) < 1e-6
+
+
+def test_submission_given_as_a_file_path(tmp_path):
+    """A submission file next to nothing in particular, named by path (not importable by name)."""
+    sub = tmp_path / "my submission.py"   # a name no import statement could spell
+    sub.write_text("from kernel_b200.tasks.gemm_rs.submission import custom_kernel\n")
+    rc, log, err = _run(["test", "@tests", "--backend", "gloo", "--submission", str(sub)], RS + "\n", tmp_path)
+    assert rc == 0, err
+    assert log["check"] == "pass"
+    rc, log, err = _run(["test", "@tests", "--backend", "gloo", "--submission", str(tmp_path / "absent.py")], RS + "\n", tmp_path)
+    assert rc == 112 and "not found" in log["test.0.error"]
