@@ -41,6 +41,7 @@ def _rs(rank, world, M, Nn, Kl, with_bias, calls):
     (2, 256, 264, 72, True),     # one row block per rank, N tail
     (3, 192, 512, 40, False),    # rows per rank 64: two owners share a row block, M tail
     (4, 1024, 256, 24, True),    # several row blocks per rank
+    (8, 512, 264, 16, True),     # the flagship world size: 64 rows per rank, two owners per row block
 ])
 def test_gemm_rs_over_host_heap(world, M, Nn, Kl, with_bias):
     assert all(run_ranks(_rs, world, M, Nn, Kl, with_bias, 3))
@@ -75,6 +76,7 @@ def _ag(rank, world, M, Nl, K, with_bias, calls):
     (2, 256, 264, 72, True),
     (3, 192, 256, 40, False),    # rows per rank 64: a row block waits for two sources
     (4, 1024, 128, 24, True),
+    (8, 1024, 72, 16, False),    # the flagship world size: one row block per rank
 ])
 def test_ag_gemm_over_host_heap(world, M, Nl, K, with_bias):
     assert all(run_ranks(_ag, world, M, Nl, K, with_bias, 3))

@@ -110,7 +110,8 @@ def _moe_over_host_heap(rank, world, dtype_name):
     from kernel_b200.ops.dispatch_combine import SCALE_EXPERT, MoEAllToAll, expert_scale_vector
 
     dtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[dtype_name]
-    E, k, H, T = 18, 4, 64, 5 + rank  # token counts differ between ranks
+    E = 18 if 18 % world == 0 else 3 * world
+    k, H, T = 4, 64, 5 + rank  # token counts differ between ranks
     ctx = MoEAllToAll(E, k, H, 16, dtype=dtype, device="cpu")
     assert ctx.host_heap and ctx.heap.backend == "host"
     g = torch.Generator().manual_seed(100 + rank)
@@ -130,6 +131,10 @@ def _moe_over_host_heap(rank, world, dtype_name):
 @pytest.mark.parametrize("dtype_name", ["fp32", "bf16", "fp16"])
 def test_moe_round_trip_over_host_heap(dtype_name):
     assert all(run_ranks(_moe_over_host_heap, 3, dtype_name))
+
+
+def test_moe_round_trip_over_host_heap_world8():
+    assert all(run_ranks(_moe_over_host_heap, 8, "bf16", timeout=300))
 
 
 def _moe_with_absent_rank(rank, world):
