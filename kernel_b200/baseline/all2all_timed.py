@@ -15,6 +15,8 @@ import atexit
 import os
 import sys
 
+import torch.distributed as dist
+
 from . import all2all as _impl
 from ..utils.timing import format_summary
 
@@ -34,7 +36,7 @@ def custom_kernel(data):
 def _report() -> None:
     for dev, tm in _impl._timers.items():
         if tm.summary():
-            rank = os.environ.get("RANK", getattr(dev, "index", 0) or 0)
+            rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else os.environ.get("RANK", dev.index or 0)
             print(format_summary(tm, rank), file=sys.stderr, flush=True)
 
 
