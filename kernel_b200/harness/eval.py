@@ -200,8 +200,14 @@ class _Group:
         import torch.distributed as dist
 
         try:
-            if self.sub is not None and hasattr(self.sub, "release_contexts") and exc_type is None:
-                self.sub.release_contexts()
+            if exc_type is None:
+                # the evaluated module, then the built-in submissions a user module may wrap
+                mods = [self.sub] + [sys.modules.get(f"kernel_b200.tasks.{t}.submission") for t in ("all2all", "gemm_rs", "ag_gemm")]
+                seen = set()
+                for m in mods:
+                    if m is not None and id(m) not in seen and hasattr(m, "release_contexts"):
+                        seen.add(id(m))
+                        m.release_contexts()
         finally:
             dist.destroy_process_group()
         return False

@@ -239,11 +239,16 @@ class SymmHeap:
                 raise N.SymmTimeoutError(N.KB_ERR_TIMEOUT, msg)
             raise N.NativeError(N.KB_ERR_ARG, msg)
 
-    def close(self) -> None:
+    def close(self, collective: bool = True) -> None:
+        """Unmaps and frees the segments.  Collective by default (a control-plane
+        barrier first: nobody unmaps while a peer may still touch the memory);
+        ``collective=False`` is for a heap whose process group is gone, when no
+        peer can be using it any more."""
         if self._h:
             if self.backend != "host" and torch.cuda.is_available():
                 torch.cuda.synchronize(self.device)
-            self._control_barrier()  # nobody unmaps while a peer may still touch the memory
+            if collective:
+                self._control_barrier()
             self._lib.kb_symm_destroy(self._h)
             self._h = C.c_void_p()
 

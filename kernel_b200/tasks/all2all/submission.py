@@ -15,10 +15,13 @@ from .task import input_t, output_t
 _contexts: dict = {}
 
 
+def _group():
+    return dist.group.WORLD if dist.is_available() and dist.is_initialized() else None
+
+
 def _group_key():
-    if dist.is_available() and dist.is_initialized():
-        return id(dist.group.WORLD)
-    return None
+    g = _group()
+    return id(g) if g is not None else None
 
 
 def get_context(cfg, world_size: int, device: torch.device) -> MoEAllToAll:
@@ -28,15 +31,19 @@ def get_context(cfg, world_size: int, device: torch.device) -> MoEAllToAll:
     if ctx is None:
         ctx = MoEAllToAll(cfg.num_experts, cfg.experts_per_token, cfg.hidden_dim, cfg.max_num_tokens,
                           dtype=cfg.in_dtype, device=device)
+        ctx.process_group = _group()  # kept alive with the entry: the id in the key cannot be reused meanwhile
         _contexts[key] = ctx
     return ctx
 
 
 def release_contexts() -> None:
-    """Frees cached workspaces (collective; call before destroying the process group)."""
+    """Frees cached workspaces.  Collective for the contexts of the current process
+    group (call before destroying it); contexts left over from an earlier group
+    are freed locally."""
+    current = _group()
     for ctx in _contexts.values():
         if ctx.heap is not None:
-            ctx.heap.close()
+            ctx.heap.close(collective=ctx.process_group is current)
     _contexts.clear()
 
 

@@ -15,8 +15,13 @@ from .task import input_t, output_t
 _contexts: dict = {}
 
 
+def _group():
+    return dist.group.WORLD if dist.is_available() and dist.is_initialized() else None
+
+
 def _group_key():
-    return id(dist.group.WORLD) if dist.is_available() and dist.is_initialized() else None
+    g = _group()
+    return id(g) if g is not None else None
 
 
 def get_context(M: int, N: int, device: torch.device) -> GemmRS:
@@ -24,14 +29,19 @@ def get_context(M: int, N: int, device: torch.device) -> GemmRS:
     ctx = _contexts.get(key)
     if ctx is None:
         ctx = GemmRS(M, N, device=device)
+        ctx.process_group = _group()  # kept alive with the entry: the id in the key cannot be reused meanwhile
         _contexts[key] = ctx
     return ctx
 
 
 def release_contexts() -> None:
+    """Frees cached workspaces.  Collective for the contexts of the current process
+    group (call before destroying it); contexts left over from an earlier group
+    are freed locally."""
+    current = _group()
     for ctx in _contexts.values():
         if ctx.heap is not None:
-            ctx.heap.close()
+            ctx.heap.close(collective=ctx.process_group is current)
     _contexts.clear()
 
 

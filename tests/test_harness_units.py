@@ -67,3 +67,32 @@ def test_wrap_check_accepts_both_return_styles():
 
     assert E.wrap_check(Old, None, None) == (True, "")
     assert E.wrap_check(New, None, None) == (False, "mismatch")
+
+
+def test_cached_contexts_pin_their_process_group_and_stale_ones_close_locally(monkeypatch):
+    """A cached context keeps its process-group object alive (so the id in the cache
+    key cannot be reused by a later group) and, once that group is gone, is freed
+    without a collective barrier."""
+    import torch
+
+    from kernel_b200.tasks.all2all import reference as R
+    from kernel_b200.tasks.all2all import submission as S
+
+    S.release_contexts()
+    data = R.generate_input(4, 2, 16, 4, 1, 0, 1, dtype="fp32", fixed_tokens=True, device="cpu")
+    ctx = S.get_context(data[0], 1, torch.device("cpu"))
+    assert S.get_context(data[0], 1, torch.device("cpu")) is ctx            # cached
+    assert hasattr(ctx, "process_group") and ctx.process_group is None      # no group in this process
+    calls = []
+    real_close = ctx.heap.close
+    monkeypatch.setattr(ctx.heap, "close", lambda collective=True: (calls.append(collective), real_close(collective=collective)))
+    ctx.process_group = object()                                            # as if created under a group that no longer exists
+    S.release_contexts()
+    assert calls == [False] and S._contexts == {}
+    ctx2 = S.get_context(data[0], 1, torch.device("cpu"))
+    assert ctx2 is not ctx
+    calls2 = []
+    real_close2 = ctx2.heap.close
+    monkeypatch.setattr(ctx2.heap, "close", lambda collective=True: (calls2.append(collective), real_close2(collective=collective)))
+    S.release_contexts()
+    assert calls2 == [True]
