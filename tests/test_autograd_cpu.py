@@ -158,3 +158,20 @@ def test_expert_major_rows_order():
     assert n_e == [3, 3, 1]
     # expert 0: src0 rows 0,1 and src1 row 0; expert 1: src1 rows 1..3; expert 2: src0 row 2
     assert idx.tolist() == [0, 1, 10, 11, 12, 13, 2]
+
+
+def _demo(rank, world, moe):
+    from kernel_b200.utils.train_demo import train
+
+    return train(steps=12, tokens=64 * world, hidden=32, ffn=64 * world, moe=moe, lr=0.05, device="cpu")
+
+
+def test_training_demo_loss_decreases_single_process():
+    losses = _demo(0, 1, True)
+    assert losses[-1] < 0.9 * losses[0] and all(b <= a * 1.02 for a, b in zip(losses, losses[1:]))
+
+
+def test_training_demo_loss_decreases_gloo_world2():
+    res = run_ranks(_demo, 2, True)
+    assert res[0] == res[1]                       # the all-reduced loss is the same number on both ranks
+    assert res[0][-1] < 0.9 * res[0][0]
