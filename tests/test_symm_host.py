@@ -160,3 +160,29 @@ def test_moe_wait_names_the_rank_that_never_arrived():
     res = run_ranks(_moe_with_absent_rank, 2, env={"KB200_WAIT_LIMIT_MS": "300"})
     assert res[1] == "absent"
     assert "rank 1 never finished its dispatch of epoch 2" in res[0]
+
+
+def test_multicast_probe_and_entry_points_fail_cleanly_without_a_device():
+    """No driver, no multicast: the probe says no and the set-up entry points refuse
+    a heap that is not a VMM heap, instead of touching the driver."""
+    lib = N.lib()
+    assert lib.kb_symm_mc_supported(0) == 0
+    h = C.c_void_p()
+    assert lib.kb_symm_create(N.BACKEND_HOST, 0, 1, 4096, 0, C.byref(h)) == N.KB_OK
+    fd = C.c_int(-1)
+    assert lib.kb_symm_mc_create(h, C.byref(fd)) == N.KB_ERR_ARG and fd.value == -1
+    assert not lib.kb_symm_mc_ptr(h)
+    lib.kb_symm_destroy(h)
+
+
+def _host_heap_with_nvls_requested(rank, world):
+    from kernel_b200.parallel.symm import SymmHeap
+
+    heap = SymmHeap(1 << 16, backend="host", nvls=True)   # asked for, not available on a host heap
+    ok = heap.mc_ptr is None and heap.backend == "host"
+    heap.close()
+    return ok
+
+
+def test_nvls_request_on_host_heap_is_ignored():
+    assert all(run_ranks(_host_heap_with_nvls_requested, 2))
