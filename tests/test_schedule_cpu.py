@@ -77,3 +77,41 @@ def test_all_gather_order_own_first_then_arrival_order(pair):
         assert chunk_index == sorted(chunk_index)
         first_round = rest[:world - 1]
         assert [b // per_rank for b in first_round] == [(rank + d) % world for d in range(1, world)]
+
+
+def test_schedule_properties_over_random_problems():
+    """Random shapes, world sizes and tile configurations: every tile exactly once; for
+    the reduce-scatter no tile holding rows of this rank comes before a tile that
+    holds none; for the all-gather the first row block visited holds own rows."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    @settings(max_examples=150, deadline=None)
+    @given(mode=st.sampled_from([PLAIN, RS, AG]), world=st.sampled_from([1, 2, 3, 4, 8, 16]), pair=st.booleans(),
+           rows_factor=st.sampled_from([8, 16, 32, 64, 128, 256, 384, 512, 1024]), extra_m=st.integers(0, 127),
+           n=st.integers(1, 40).map(lambda v: v * 104))
+    def check(mode, world, pair, rows_factor, extra_m, n):
+        M = rows_factor * world + (extra_m if mode == PLAIN else 0)   # fused modes need M divisible by world
+        rpo = M // world
+        if mode != PLAIN and world > 1 and rpo % 128 != 0 and 128 % rpo != 0:
+            return                                                     # refused by the launcher, not a schedule case
+        rows = 256 if pair else 128
+        for rank in sorted({0, world // 2, world - 1}):
+            tiles = schedule(mode, M, n, rank, world, pair)
+            if tiles is None:
+                assert pair and mode != PLAIN and world > 1 and rpo % 256 != 0
+                continue
+            mbq, nbs = -(-M // rows), -(-n // 256)
+            assert len(tiles) == mbq * nbs and len(set(tiles)) == len(tiles)
+            assert all(0 <= b < mbq and 0 <= c < nbs for b, c in tiles)
+            if world == 1 or mode == PLAIN:
+                continue
+            lo, hi = rank * rpo, (rank + 1) * rpo - 1                  # rows of this rank
+            own = [lo // rows <= b <= hi // rows for b, _ in tiles]
+            if mode == RS:
+                first_own = own.index(True)
+                assert all(own[first_own:])                            # own segment is a suffix
+            else:
+                assert own[0]                                          # the all-gather starts on rows it already has
+
+    check()
