@@ -139,13 +139,21 @@ def available() -> bool:
 
 
 def lib() -> C.CDLL:
-    """Returns the loaded library, building it first if the file is missing."""
+    """Returns the loaded library, building it first if the file is missing or older
+    than its sources (a digest check; a no-op when it is current).  A stale file is
+    still used, with a warning, on a machine that cannot rebuild it."""
     global _lib
     if _lib is None:
-        if not LIB_PATH.exists():
-            from .csrc.build import build
+        from .csrc.build import build
 
+        try:
             build()
+        except Exception as e:  # no compiler here
+            if not LIB_PATH.exists():
+                raise
+            import warnings
+
+            warnings.warn(f"libkb200.so could not be checked against its sources ({e}); using the existing file")
         _lib = C.CDLL(str(LIB_PATH))
         _declare(_lib)
     return _lib

@@ -8,6 +8,7 @@ loads on a machine without a driver.
 """
 from __future__ import annotations
 
+import fcntl
 import hashlib
 import os
 import shutil
@@ -66,8 +67,21 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     OBJ_DIR.mkdir(exist_ok=True)
     stamp = OBJ_DIR / "digest.txt"
     digest = _digest()
-    if not force and LIB_PATH.exists() and stamp.exists() and stamp.read_text() == digest:
+
+    def current() -> bool:
+        return LIB_PATH.exists() and stamp.exists() and stamp.read_text() == digest
+
+    if not force and current():
         return LIB_PATH
+    # One builder at a time: the ranks of a job may all find the library stale at once.
+    with open(OBJ_DIR / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and current():  # another process built it while this one waited
+            return LIB_PATH
+        return _build_locked(digest, stamp, verbose)
+
+
+def _build_locked(digest: str, stamp: Path, verbose: bool) -> Path:
     nvcc = _nvcc()
 
     def compile_one(rel: str) -> Path:
@@ -85,11 +99,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as pool:
         objs = list(pool.map(compile_one, _sources()))
-    link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-cudart", "static", "-lpthread", "-ldl", "-lrt"]
+    tmp = LIB_PATH.with_suffix(f".so.tmp{os.getpid()}")
+    link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp), *map(str, objs), "-cudart", "static", "-lpthread", "-ldl", "-lrt"]
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(f"$ {' '.join(link)}\n{res.stdout}{res.stderr}\n")
         raise RuntimeError("link failed")
+    os.replace(tmp, LIB_PATH)  # a process that has the old file mapped keeps it; nobody sees a half-written one
     stamp.write_text(digest)
     return LIB_PATH
 
