@@ -121,3 +121,50 @@ def test_collectives_path_still_selectable(monkeypatch):
     monkeypatch.setenv("KB200_GEMM_CPU_PATH", "collectives")
     ctx = GemmRS(128, 64, device="cpu")
     assert not ctx.host_heap and ctx.heap is None
+
+
+def _many_shapes(rank, world, seed):
+    """Both fused ops over a handful of random shapes in one set of ranks."""
+    import random
+
+    import torch.distributed as dist
+
+    from kernel_b200.ops.gemm import AGGemm, GemmRS
+
+    rnd = random.Random(seed)   # same shapes on every rank
+    bad = []
+    for case in range(6):
+        rpo = rnd.choice([8, 16, 32, 64, 128, 256])
+        M = rpo * world
+        Nn = rnd.randrange(1, 60) * 8
+        K = rnd.randrange(1, 12) * 8
+        g = torch.Generator().manual_seed(seed * 100 + case * 10 + rank)
+        # reduce-scatter: K is the local share
+        a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        w = (torch.randn(Nn, K, generator=g) / (K * world) ** 0.5).to(torch.bfloat16)
+        rs = GemmRS(M, Nn, device="cpu")
+        out = rs(a, w)
+        part = a.float() @ w.float().t()
+        mag = part.abs()
+        dist.all_reduce(part)
+        dist.all_reduce(mag)
+        sl = slice(rank * rpo, (rank + 1) * rpo)
+        if not bool(((out.float() - part[sl]).abs() <= 1e-2 + 1e-2 * mag[sl]).all()):
+            bad.append(("rs", M, Nn, K))
+        rs.heap.close()
+        # all-gather: N is the local share
+        a_local = torch.randn(rpo, K, generator=g).to(torch.bfloat16)
+        ag = AGGemm(M, K, device="cpu")
+        out = ag(a_local, w)
+        full = torch.empty(M, K, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(full, a_local)
+        if not torch.allclose(out.float(), full.float() @ w.float().t(), rtol=1e-2, atol=1e-2):
+            bad.append(("ag", M, Nn, K))
+        ag.heap.close()
+    return bad
+
+
+@pytest.mark.parametrize("world,seed", [(2, 1), (4, 2), (3, 3)])
+def test_random_shapes_over_host_heap(world, seed):
+    for bad in run_ranks(_many_shapes, world, seed, timeout=300):
+        assert bad == []
