@@ -53,6 +53,7 @@ class GemmArgs(C.Structure):
         ("status", C.c_void_p),
         ("wait_limit_ns", C.c_uint64),
         ("num_ctas", C.c_int),
+        ("mc_base", C.c_void_p),
     ]
 
 
@@ -109,7 +110,9 @@ def _declare(lib: C.CDLL) -> None:
         "kb_symm_mc_ptr": (vp, [vp]),
         "kb_symm_destroy": (i, [vp]),
         "kb_symm_host_barrier": (i, [vp, u64, u32, i]),
-        "kb_wait_flags": (i, [vp, i, u32, u64, vp, vp]),
+        "kb_multimem_store": (i, [vp, vp, u64, vp]),
+        "kb_multimem_reduce_bf16": (i, [vp, vp, u64, vp]),
+        "kb_wait_flags": (i, [vp, i, i, u32, u64, vp, vp]),
         "kb_device_barrier": (i, [C.POINTER(vp), u64, i, i, u32, u64, vp, vp]),
         "kb_gemm": (i, [C.POINTER(GemmArgs), vp]),
         "kb_gemm_schedule": (i, [i, i, i, i, i, i, i, C.POINTER(i), C.POINTER(i)]),
@@ -119,6 +122,12 @@ def _declare(lib: C.CDLL) -> None:
         "kb_gemm_ag_flag_bytes": (u64, [i, i]),
         "kb_gemm_ag_counter_bytes": (u64, [i, i]),
         "kb_a2a_rows_bytes": (u64, [i, i, i, i, i]),
+        "kb_a2a_flag_bytes": (u64, []),
+        "kb_a2a_sync_bytes": (u64, []),
+        "kb_a2a_flag_stride_words": (i, []),
+        "kb_a2a_post_ready": (i, [C.POINTER(A2aArgs), vp]),
+        "kb_a2a_round_trip_static": (i, [vp, vp, vp, vp, i, i, i, i, i, i, vp]),
+        "kb_a2a_static_status": (i, [vp, i, vp]),
         "kb_a2a_dispatch": (i, [C.POINTER(A2aArgs), vp]),
         "kb_a2a_expert_scale": (i, [C.POINTER(A2aArgs), vp]),
         "kb_a2a_combine": (i, [C.POINTER(A2aArgs), vp]),

@@ -30,6 +30,7 @@ SOURCES = [
     "symm/gemm_host.cpp",
     "kernels/a2a.cu",
     "kernels/gemm_sm100.cu",
+    "kernels/nvls_util.cu",
 ]
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -84,6 +84,26 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// 2-D tiled store shared -> global of one box (bulk async group of the issuing
+// thread).  Rows and columns of the box that fall outside the tensor are not
+// written.  x * elem_size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk groups still read their source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until at most N of this thread's bulk groups are incomplete.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // ------------------------------------------------------------- tcgen05 ----
 // TMEM allocation: whole warp, `ncols` a power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t ncols) {
@@ -250,6 +270,25 @@ __device__ __forceinline__ void st_sys_v4(void* p, const uint4& v) {
                "r"(v.w)
                : "memory");
 }
+// ------------------------------------------------- NVLS (multimem) traffic ----
+// `mc` is an address inside the multicast mapping of the symmetric heap: a store
+// lands at the same offset of every rank's segment, a ld_reduce returns the sum
+// of the values at that offset of every rank's segment, added in the switch.
+__device__ __forceinline__ void multimem_st_v4(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+// Eight bf16 values per call, accumulated in fp32 inside the switch, returned as bf16 pairs.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+
 // Streaming read of data that is read-only for the whole kernel.
 __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
   uint4 v;
@@ -259,25 +298,51 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
   return v;
 }
 
+// Device-scope counterparts for words that only threads of this GPU touch.
+__device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_relaxed_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+
 // Spin on a 32-bit flag until it reaches `want` (flags only grow).  Returns
 // false if `limit_ns` passes first.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint64_t limit_ns) {
-  // Polls with relaxed loads and pays for one acquire fence once the flag is
-  // there.  The pause between polls doubles up to half a microsecond: hundreds
-  // of CTAs poll words of the same cache line, and an unthrottled spin takes
-  // L2 bandwidth away from the very stores it is waiting for.
-  if (static_cast<int32_t>(ld_relaxed_sys_u32(flag) - want) >= 0) {
-    fence_sys();
+//
+// Polls with relaxed loads and pays for one acquire fence once the flag is
+// there.  The pause between polls doubles up to `max_pause_ns`: where many
+// CTAs poll words of the same cache line an unthrottled spin takes L2 bandwidth
+// away from the very stores it is waiting for.  A single poller of a line passes
+// 0 and spins without pausing (a pause costs about a microsecond of reaction
+// time).  `sys` false: the word is written by this GPU only, device scope is
+// enough for the polls and the fence.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint64_t limit_ns,
+                                             uint32_t max_pause_ns = 512, bool sys = true) {
+  auto poll = [&]() -> bool {
+    const uint32_t v = sys ? ld_relaxed_sys_u32(flag) : ld_relaxed_gpu_u32(flag);
+    return static_cast<int32_t>(v - want) >= 0;
+  };
+  auto acquire = [&]() {
+    if (sys) fence_sys();
+    else fence_gpu();
+  };
+  if (poll()) {
+    acquire();
     return true;
   }
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   uint32_t pause = 32;
   for (;;) {
-    __nanosleep(pause);
-    if (pause < 512) pause *= 2;
-    if (static_cast<int32_t>(ld_relaxed_sys_u32(flag) - want) >= 0) {
-      fence_sys();
+    if (max_pause_ns != 0) {
+      __nanosleep(pause);
+      if (pause < max_pause_ns) pause *= 2;
+    }
+    if (poll()) {
+      acquire();
       return true;
     }
     if ((++spins & 0x3fu) == 0 && globaltimer_ns() - t0 > limit_ns) return false;

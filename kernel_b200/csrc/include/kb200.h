@@ -68,15 +68,22 @@ int kb_symm_mc_join(KbSymmHeap* h, int fd_from_rank0);
 int kb_symm_mc_bind(KbSymmHeap* h);
 void* kb_symm_mc_ptr(const KbSymmHeap* h);
 int kb_symm_destroy(KbSymmHeap* h);
+// NVLS primitives over the multicast mapping (kernels/nvls_util.cu); bytes a multiple of 16.
+// Store: every rank's segment receives `bytes` from local `src` at the offset `mc_dst` has in the mapping.
+// Reduce: local `dst` receives the sum over all ranks of the bf16 values at `mc_src` (fp32 accumulation).
+int kb_multimem_store(void* mc_dst, const void* src, uint64_t bytes, void* stream);
+int kb_multimem_reduce_bf16(void* dst, const void* mc_src, uint64_t bytes, void* stream);
 
 // Host-side epoch barrier over a KB_BACKEND_HOST heap (CPU atomics on the
 // shared segment); `pad_off` is the byte offset of a world*4-byte flag pad.
 int kb_symm_host_barrier(KbSymmHeap* h, uint64_t pad_off, uint32_t epoch, int timeout_ms);
 
 // ---- device utilities -------------------------------------------------------
-// Bounded wait kernel: waits until flags[i] >= want for i < n, or gives up
+// Bounded wait kernel: waits until flag i >= want for i < n, or gives up
 // after limit_ns and records KB_DEV_TIMEOUT_FLAG in status.
-int kb_wait_flags(const uint32_t* flags, int n, uint32_t want, uint64_t limit_ns, uint32_t* status, void* stream);
+// Flag i is the word flags[i * stride_words].
+int kb_wait_flags(const uint32_t* flags, int n, int stride_words, uint32_t want, uint64_t limit_ns, uint32_t* status,
+                  void* stream);
 // Cross-rank device barrier: post `epoch` into slot `rank` of every peer's pad,
 // then wait for all `world` slots of the local pad.
 int kb_device_barrier(void* const* peer_bases, uint64_t pad_off, int rank, int world, uint32_t epoch,
@@ -100,12 +107,14 @@ typedef struct KbGemmArgs {
   int rank, world;
   uint32_t epoch;          // strictly increasing per call on a workspace
   void* peer_base[KB_MAX_WORLD];  // symmetric heap bases (RS/AG)
-  uint64_t data_off;       // RS: staging [2][world][M/world][N]; AG: gather [2][M][K]
+  uint64_t data_off;       // RS: this rank's partial product, bf16 [2][M][N], pulled by the row owners; AG: gather [2][M][K]
   uint64_t flag_off;       // RS: flags [2][world][tiles]; AG: flags [2][world][m_blocks]
   uint64_t counter_off;    // AG: local push counters [world][chunks] (uint32)
   uint32_t* status;        // device uint32[8]
   uint64_t wait_limit_ns;  // bound for every device-side wait
   int num_ctas;            // 0 = one per SM
+  void* mc_base;           // multicast mapping of the heap (kb_symm_mc_ptr) or NULL: with it the RS reduction uses
+                           // multimem.ld_reduce and the AG pushes multimem.st; without it peer loads and stores
 } KbGemmArgs;
 
 int kb_gemm(const KbGemmArgs* args, void* stream);
@@ -138,8 +147,9 @@ typedef struct KbA2aArgs {
   uint64_t recv_off;    // [world][max_tokens*topk][H] rows received from each source
   uint64_t y_off;       // same shape: expert outputs, pulled by the sources
   uint64_t count_off;   // int32 [world][experts_per_rank]
-  uint64_t flag_off;    // uint32 [2][world]: dispatch-done and y-ready epochs
-  uint64_t sync_off;    // local uint32[4] block counters
+  uint64_t flag_off;    // kb_a2a_flag_bytes(): dispatch-done and y-ready epochs, flag (phase, source) at word
+                        // (phase * KB_MAX_WORLD + source) * kb_a2a_flag_stride_words(), one 128-byte line each
+  uint64_t sync_off;    // kb_a2a_sync_bytes(): local block counters and the arrival words of the fused launch
   int scale_mode;       // 0: y = x; 1: y = x*(1+rank); 2: y = x*(expert_id+1)/num_experts
   uint32_t* status;
   uint64_t wait_limit_ns;
@@ -148,6 +158,11 @@ typedef struct KbA2aArgs {
 } KbA2aArgs;
 
 uint64_t kb_a2a_rows_bytes(int world, int max_tokens, int topk, int hidden, int elem_bytes);
+uint64_t kb_a2a_flag_bytes(void);
+uint64_t kb_a2a_sync_bytes(void);
+int kb_a2a_flag_stride_words(void);
+// Posts this rank's y-ready flag of args->epoch on every rank (after the caller's own expert computation).
+int kb_a2a_post_ready(const KbA2aArgs* a, void* stream);
 int kb_a2a_dispatch(const KbA2aArgs* a, void* stream);
 int kb_a2a_expert_scale(const KbA2aArgs* a, void* stream);
 int kb_a2a_combine(const KbA2aArgs* a, void* stream);

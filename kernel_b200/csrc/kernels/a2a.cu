@@ -33,8 +33,12 @@ namespace {
 constexpr int A2A_THREADS = 256;
 constexpr int MAX_EXPERTS = 1024;
 constexpr int MAX_ENT_PER_CTA = 2048;
+// Every (phase, source) flag sits on a 128-byte line of its own: a peer's flag
+// store never queues behind polls of another source's flag.
+constexpr int FLAG_STRIDE_WORDS = 32;
+constexpr int GO_WORD_OFF = 32;   // sync region: words [0..3] block counters, [32..47] and [64..79] arrival words
 
-enum Site : uint32_t { SITE_DISP_IDX = 11, SITE_EXP_FLAG = 12, SITE_COMB_FLAG = 13, SITE_COMB_SLOT = 14 };
+enum Site : uint32_t { SITE_DISP_IDX = 11, SITE_EXP_FLAG = 12, SITE_COMB_FLAG = 13, SITE_COMB_SLOT = 14, SITE_POLLER = 15 };
 
 struct A2aParams {
   int rank, world, E, El, k, H, T, cap;
@@ -55,8 +59,10 @@ struct A2aParams {
 };
 
 // Phase stamps (nanoseconds of the global timer) written by thread 0 of CTA 0.
-enum Stamp { ST_ENTRY = 0, ST_SLOTS = 1, ST_PUSHED = 2, ST_DISPATCH_FLAG = 3, ST_EXPERT_GO = 4, ST_COUNTS = 5, ST_EXPERT_ROWS = 6,
-             ST_EXPERT_FLAG = 7, ST_COMBINE_GO = 8, ST_DONE = 9 };
+// Words 10 and 11 hold the time that CTA spent inside the arrival waits of the
+// expert pass and of the combine.
+enum Stamp { ST_ENTRY = 0, ST_SLOTS = 1, ST_PUSHED = 2, ST_DISPATCH_FLAG = 3, ST_EXPERT_GO = 4, ST_EXPERT_ROWS = 5,
+             ST_EXPERT_FLAG = 6, ST_COMBINE_GO = 7, ST_DONE = 8, ST_WAITED_EXPERT = 10, ST_WAITED_COMBINE = 11 };
 __device__ __forceinline__ void stamp(const A2aParams& p, int which) {
   if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[which] = kb::globaltimer_ns();
 }
@@ -69,25 +75,69 @@ __device__ __forceinline__ int32_t* counts_ptr(const A2aParams& p, int on_rank, 
   return reinterpret_cast<int32_t*>(p.peer_base[on_rank] + p.count_off) + static_cast<size_t>(src) * p.El;
 }
 __device__ __forceinline__ uint32_t* flag_ptr(const A2aParams& p, int on_rank, int which, int src) {
-  return reinterpret_cast<uint32_t*>(p.peer_base[on_rank] + p.flag_off) + which * p.world + src;
+  return reinterpret_cast<uint32_t*>(p.peer_base[on_rank] + p.flag_off) +
+         static_cast<size_t>(which * KB_MAX_WORLD + src) * FLAG_STRIDE_WORDS;
+}
+// Local arrival word of (phase, source), published by the poller CTA of a fused launch.
+__device__ __forceinline__ uint32_t* go_ptr(const A2aParams& p, int which, int src) {
+  return reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.sync_off) + GO_WORD_OFF * (1 + which) + src;
+}
+// With one rank nothing leaves this GPU and device scope is enough.
+__device__ __forceinline__ void fence_for(const A2aParams& p) {
+  if (p.world == 1) __threadfence();
+  else kb::fence_sys();
+}
+
+// Publishes this rank's flag of phase `which` on rank `dst` (one thread per destination).
+__device__ __forceinline__ void post_flag(const A2aParams& p, int dst, int which) {
+  if (p.world == 1) kb::st_release_gpu_u32(flag_ptr(p, dst, which, p.rank), p.epoch);
+  else kb::st_release_sys_u32(flag_ptr(p, dst, which, p.rank), p.epoch);
 }
 
 // Last-block-done: returns true in exactly one CTA (the last to arrive) once
 // the writes of all CTAs are ordered before it.
-__device__ __forceinline__ bool last_block_done(uint32_t* counter, uint32_t total) {
+__device__ __forceinline__ bool last_block_done(const A2aParams& p, uint32_t* counter, uint32_t total) {
   __shared__ uint32_t s_last;
   __syncthreads();
   if (threadIdx.x == 0) {
-    kb::fence_sys();
+    fence_for(p);
     const uint32_t old = atomicAdd(counter, 1u);
     s_last = (old == total - 1u) ? 1u : 0u;
     if (s_last) {
       *counter = 0u;  // ready for the next launch
-      kb::fence_sys();
+      fence_for(p);
     }
   }
   __syncthreads();
   return s_last != 0u;
+}
+
+// Waits until source `src` has reached phase `which` of this epoch.  In a fused
+// launch the data CTAs watch the local arrival word that the poller CTA
+// publishes (one reader per CTA of a line nobody writes remotely); otherwise
+// they watch the flag the peer writes.  One thread calls this.
+template <bool kFused>
+__device__ __forceinline__ bool wait_arrival(const A2aParams& p, int which, int src) {
+  // The arrival words are written and read on this GPU only: device scope.  What
+  // a peer wrote before its flag is ordered before the poller's system-scope
+  // acquire, hence before the poller's release of the word, hence before this read.
+  if (kFused) return kb::wait_flag_ge(go_ptr(p, which, src), p.epoch, 2 * p.limit_ns, 0, false);
+  return kb::wait_flag_ge(flag_ptr(p, p.rank, which, src), p.epoch, p.limit_ns, 256, p.world > 1);
+}
+
+// The poller CTA of a fused launch: thread s watches the two flags source s
+// sends and republishes each as a local arrival word.  It is the only reader of
+// the lines the peers write.  After a time-out it reports and publishes anyway,
+// so that the data CTAs do not each run into their own limit.
+__device__ __forceinline__ void poller_body(const A2aParams& p) {
+  const int s = threadIdx.x;
+  if (s >= p.world) return;
+  for (int which = 0; which < 2; ++which) {
+    if (!kb::wait_flag_ge(flag_ptr(p, p.rank, which, s), p.epoch, p.limit_ns, 0, p.world > 1)) {
+      kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_POLLER, (uint32_t)(which * KB_MAX_WORLD + s), p.epoch);
+    }
+    kb::st_release_gpu_u32(go_ptr(p, which, s), p.epoch);
+  }
 }
 
 // ------------------------------------------------------------------ dispatch ----
@@ -101,13 +151,47 @@ __device__ __forceinline__ void unit_ranges(const A2aParams& p, int& t0, int& t1
   const int v_per = (p.vecs + p.h_splits - 1) / p.h_splits;
   v0 = min(hs * v_per, p.vecs);
   v1 = min(v0 + v_per, p.vecs);
-  if (blockIdx.x >= p.tok_groups * p.h_splits) {  // surplus CTAs of a fused launch
+  if (blockIdx.x >= p.tok_groups * p.h_splits) {  // surplus CTAs
     t0 = t1 = p.T;
     v0 = v1 = 0;
   }
 }
 
-__device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh) {
+// off[e] = entries of the experts before e on e's owner rank: an exclusive block
+// scan over all experts (four per thread), minus the scan value at the owner's
+// first expert.  `tmp` holds E words.
+__device__ __forceinline__ void expert_offsets(const int32_t* tot, int32_t* off, int32_t* tmp, int E, int El) {
+  __shared__ int32_t s_warp[A2A_THREADS / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int v[4];
+  int sum = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = tid * 4 + j;
+    v[j] = e < E ? tot[e] : 0;
+    sum += v[j];
+  }
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  int run = incl - sum;
+  for (int wv = 0; wv < warp; ++wv) run += s_warp[wv];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = tid * 4 + j;
+    if (e < E) tmp[e] = run;
+    run += v[j];
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) off[e] = tmp[e] - tmp[(e / El) * El];
+}
+
+__device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh, int nworkers) {
   int32_t* tot = sh;               // [E] entries per expert, whole rank
   int32_t* pre = tot + p.E;        // [E] entries per expert before this CTA's tokens
   int32_t* off = pre + p.E;        // [E] first slot of the expert inside its owner's region
@@ -126,22 +210,30 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh) {
     pre[e] = 0;
   }
   __syncthreads();
-  for (int i = tid; i < total_ent; i += blockDim.x) {
-    const int e = p.idx[i];
-    if (e < 0 || e >= p.E) {
-      kb::report_status(p.status, KB_DEV_BAD_INDEX, SITE_DISP_IDX, (uint32_t)i, p.epoch);
-      continue;
+  // Eight entries per thread are fetched before any is counted: one memory
+  // latency per eight entries instead of one per entry.
+  for (int i0 = tid; i0 < total_ent; i0 += 8 * blockDim.x) {
+    int ev[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * blockDim.x;
+      ev[u] = i < total_ent ? __ldg(p.idx + i) : 0;
     }
-    atomicAdd(&tot[e], 1);
-    if (i < t0 * p.k) atomicAdd(&pre[e], 1);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * blockDim.x;
+      if (i >= total_ent) continue;
+      const int e = ev[u];
+      if (e < 0 || e >= p.E) {
+        kb::report_status(p.status, KB_DEV_BAD_INDEX, SITE_DISP_IDX, (uint32_t)i, p.epoch);
+        continue;
+      }
+      atomicAdd(&tot[e], 1);
+      if (i < t0 * p.k) atomicAdd(&pre[e], 1);
+    }
   }
   __syncthreads();
-  for (int e = tid; e < p.E; e += blockDim.x) {
-    const int first = (e / p.El) * p.El;
-    int acc = 0;
-    for (int j = first; j < e; ++j) acc += tot[j];
-    off[e] = acc;
-  }
+  expert_offsets(tot, off, ent_slot, p.E, p.El);  // ent_slot is free until the ranking below
   for (int i = tid; i < n_ent; i += blockDim.x) ent_e[i] = p.idx[t0 * p.k + i];
   __syncthreads();
   // Rank of an entry among earlier entries of the same expert inside this
@@ -199,15 +291,15 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh) {
     }
   }
   uint32_t* sync = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.sync_off);
-  if (last_block_done(&sync[0], gridDim.x)) {
-    if (tid < p.world) kb::st_release_sys_u32(flag_ptr(p, tid, 0, p.rank), p.epoch);  // threads other than 0 need their own release
+  if (last_block_done(p, &sync[0], nworkers)) {
+    if (tid < p.world) post_flag(p, tid, 0);  // every posting thread releases for itself
   }
   stamp(p, ST_DISPATCH_FLAG);
 }
 
 __global__ void __launch_bounds__(A2A_THREADS) a2a_dispatch_kernel(const A2aParams p) {
   extern __shared__ int32_t sh[];
-  dispatch_body(p, sh);
+  dispatch_body(p, sh, gridDim.x);
 }
 
 // -------------------------------------------------------------- expert scale ----
@@ -266,86 +358,90 @@ struct Vec16<float> {
   }
 };
 
-template <typename T>
-__device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh) {
-  int32_t* incl = sh;                        // [world][El] inclusive prefix of counts per source
-  int32_t* src_end = incl + p.world * p.El;  // [world] inclusive prefix of per-source totals
+// The simulated expert, source by source in arrival order of a ring that starts
+// at this rank (whose own rows are there first): a source's rows are scaled as
+// soon as that source's dispatch flag is seen, while later sources may still be
+// sending.  Rows of one source are dealt round-robin to the data CTAs, starting
+// at a CTA that depends on the source so that remainders spread out.
+template <typename T, bool kFused>
+__device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh, int nworkers) {
+  int32_t* incl = sh;  // [El] inclusive prefix of the current source's counts
   const int tid = threadIdx.x;
-
-  if (tid < p.world) {
-    if (!kb::wait_flag_ge(flag_ptr(p, p.rank, 0, tid), p.epoch, p.limit_ns)) {
-      kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_EXP_FLAG, (uint32_t)tid, p.epoch);
-    }
-  }
-  __syncthreads();
-  stamp(p, ST_EXPERT_GO);
-  // All counts are fetched in parallel (one independent load per thread), then
-  // scanned in shared memory.
-  const int32_t* counts = counts_ptr(p, p.rank, 0);
-  for (int i = tid; i < p.world * p.El; i += blockDim.x) {
-    int v = static_cast<int>(kb::ld_relaxed_sys_u32(reinterpret_cast<const uint32_t*>(counts + i)));
-    incl[i] = v < 0 ? 0 : v;
-  }
-  __syncthreads();
-  if (tid < p.world) {
-    int acc = 0;
-    for (int le = 0; le < p.El; ++le) {
-      acc += incl[tid * p.El + le];
-      if (acc > p.cap) acc = p.cap;
-      incl[tid * p.El + le] = acc;
-    }
-  }
-  __syncthreads();
-  if (tid == 0) {
-    int acc = 0;
-    for (int s = 0; s < p.world; ++s) {
-      acc += incl[s * p.El + p.El - 1];
-      src_end[s] = acc;
-    }
-  }
-  __syncthreads();
-  stamp(p, ST_COUNTS);
-  const int total_rows = src_end[p.world - 1];
-  for (int g = blockIdx.x; g < total_rows; g += gridDim.x) {
-    int s = 0;
-    while (src_end[s] <= g) ++s;
-    const int row = g - (s ? src_end[s - 1] : 0);
-    // first local expert whose inclusive prefix exceeds row
-    int lo = 0, hi = p.El - 1;
-    const int32_t* in = incl + s * p.El;
-    while (lo < hi) {
-      const int mid = (lo + hi) >> 1;
-      if (in[mid] > row) hi = mid; else lo = mid + 1;
-    }
-    float scale = 1.0f;
-    if (p.scale_mode == 1) scale = static_cast<float>(1 + p.rank);
-    if (p.scale_mode == 2) scale = static_cast<float>(p.rank * p.El + lo + 1) / static_cast<float>(p.E);
-    const uint4* src = reinterpret_cast<const uint4*>(rows_ptr(p, p.rank, p.recv_off, s, row));
-    uint4* dst = reinterpret_cast<uint4*>(rows_ptr(p, p.rank, p.y_off, s, row));
-    for (int vb = tid; vb < p.vecs; vb += 4 * blockDim.x) {
-      uint4 in[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {  // all loads of this thread first: one latency per row
-        const int v = vb + u * blockDim.x;
-        if (v < p.vecs) in[u] = kb::ld_sys_v4(src + v);
+  const int lane = tid & 31;
+  uint64_t waited = 0;
+  for (int si = 0; si < p.world; ++si) {
+    const int s = (p.rank + si) % p.world;
+    if (tid == 0) {
+      const uint64_t w0 = (p.trace != nullptr && blockIdx.x == 0) ? kb::globaltimer_ns() : 0;
+      if (!wait_arrival<kFused>(p, 0, s)) {
+        kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_EXP_FLAG, (uint32_t)s, p.epoch);
       }
+      if (p.trace != nullptr && blockIdx.x == 0) waited += kb::globaltimer_ns() - w0;
+    }
+    __syncthreads();
+    if (si == 0) stamp(p, ST_EXPERT_GO);
+    // Counts of this source -> clamped inclusive prefix, by one warp.
+    if (tid < 32) {
+      const int32_t* counts = counts_ptr(p, p.rank, s);
+      int carry = 0;
+      for (int base = 0; base < p.El; base += 32) {
+        const int le = base + lane;
+        int v = 0;
+        if (le < p.El) v = static_cast<int>(kb::ld_relaxed_sys_u32(reinterpret_cast<const uint32_t*>(counts + le)));
+        if (v < 0) v = 0;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int v = vb + u * blockDim.x;
-        if (v < p.vecs) {
-          float f[Vec16<T>::N];
-          Vec16<T>::load(in[u], f);
+        for (int o = 1; o < 32; o <<= 1) {
+          const int n = __shfl_up_sync(0xffffffffu, v, o);
+          if (lane >= o) v += n;
+        }
+        v += carry;
+        if (v > p.cap) v = p.cap;
+        if (le < p.El) incl[le] = v;
+        carry = __shfl_sync(0xffffffffu, v, 31);
+      }
+    }
+    __syncthreads();
+    const int rows = incl[p.El - 1];
+    const int first = static_cast<int>((blockIdx.x + 37u * static_cast<unsigned>(s)) % static_cast<unsigned>(nworkers));
+    for (int row = first; row < rows; row += nworkers) {
+      // first local expert whose inclusive prefix exceeds row
+      int lo = 0, hi = p.El - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (incl[mid] > row) hi = mid; else lo = mid + 1;
+      }
+      float scale = 1.0f;
+      if (p.scale_mode == 1) scale = static_cast<float>(1 + p.rank);
+      if (p.scale_mode == 2) scale = static_cast<float>(p.rank * p.El + lo + 1) / static_cast<float>(p.E);
+      const uint4* src = reinterpret_cast<const uint4*>(rows_ptr(p, p.rank, p.recv_off, s, row));
+      uint4* dst = reinterpret_cast<uint4*>(rows_ptr(p, p.rank, p.y_off, s, row));
+      for (int vb = tid; vb < p.vecs; vb += 4 * blockDim.x) {
+        uint4 in[4];
 #pragma unroll
-          for (int i = 0; i < Vec16<T>::N; ++i) f[i] *= scale;
-          dst[v] = Vec16<T>::store(f);
+        for (int u = 0; u < 4; ++u) {  // all loads of this thread first: one latency per row
+          const int v = vb + u * blockDim.x;
+          if (v < p.vecs) in[u] = kb::ld_sys_v4(src + v);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int v = vb + u * blockDim.x;
+          if (v < p.vecs) {
+            float f[Vec16<T>::N];
+            Vec16<T>::load(in[u], f);
+#pragma unroll
+            for (int i = 0; i < Vec16<T>::N; ++i) f[i] *= scale;
+            dst[v] = Vec16<T>::store(f);
+          }
         }
       }
     }
+    __syncthreads();  // incl is rewritten for the next source
   }
+  if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) p.trace[ST_WAITED_EXPERT] = waited;
   stamp(p, ST_EXPERT_ROWS);
   uint32_t* sync = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.sync_off);
-  if (last_block_done(&sync[1], gridDim.x)) {
-    if (tid < p.world) kb::st_release_sys_u32(flag_ptr(p, tid, 1, p.rank), p.epoch);
+  if (last_block_done(p, &sync[1], nworkers)) {
+    if (tid < p.world) post_flag(p, tid, 1);
   }
   stamp(p, ST_EXPERT_FLAG);
 }
@@ -353,53 +449,67 @@ __device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh) {
 template <typename T>
 __global__ void __launch_bounds__(A2A_THREADS) a2a_expert_kernel(const A2aParams p) {
   extern __shared__ int32_t sh[];
-  expert_body<T>(p, sh);
+  expert_body<T, false>(p, sh, gridDim.x);
 }
 
 // ------------------------------------------------------------------- combine ----
-template <typename T>
+template <typename T, bool kFused>
 __device__ __forceinline__ void combine_body(const A2aParams& p) {
   const int tid = threadIdx.x;
+  const uint64_t w0 = (p.trace != nullptr && blockIdx.x == 0 && tid == 0) ? kb::globaltimer_ns() : 0;
   if (tid < p.world) {
-    if (!kb::wait_flag_ge(flag_ptr(p, p.rank, 1, tid), p.epoch, p.limit_ns)) {
+    if (!wait_arrival<kFused>(p, 1, tid)) {
       kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_COMB_FLAG, (uint32_t)tid, p.epoch);
     }
   }
   __syncthreads();
+  if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) p.trace[ST_WAITED_COMBINE] = kb::globaltimer_ns() - w0;
   stamp(p, ST_COMBINE_GO);
   int t0, t1, v0, v1, hs;
   unit_ranges(p, t0, t1, v0, v1, hs);
+  // Two 16-byte vectors per thread and iteration: up to sixteen peer loads in
+  // flight, accumulated in fixed k order.
   for (int t = t0; t < t1; ++t) {
-    for (int v = v0 + tid; v < v1; v += blockDim.x) {
-      float acc[Vec16<T>::N];
+    for (int vb = v0 + tid; vb < v1; vb += 2 * blockDim.x) {
+      float acc[2][Vec16<T>::N];
 #pragma unroll
-      for (int i = 0; i < Vec16<T>::N; ++i) acc[i] = 0.f;
+      for (int b = 0; b < 2; ++b) {
+#pragma unroll
+        for (int i = 0; i < Vec16<T>::N; ++i) acc[b][i] = 0.f;
+      }
       for (int k0 = 0; k0 < p.k; k0 += 8) {
-        uint4 u[8];
+        uint4 u[2][8];
         float wk[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int kk = k0 + j;
           wk[j] = 0.f;
-          u[j] = make_uint4(0, 0, 0, 0);
+          u[0][j] = u[1][j] = make_uint4(0, 0, 0, 0);
           if (kk < p.k) {
             const int e = p.idx[t * p.k + kk];
             const int slot = p.slots[t * p.k + kk];
             if (e >= 0 && e < p.E && slot >= 0 && slot < p.cap) {
               wk[j] = p.w[t * p.k + kk];
-              u[j] = kb::ld_sys_v4(reinterpret_cast<const uint4*>(rows_ptr(p, e / p.El, p.y_off, p.rank, slot)) + v);
+              const uint4* row = reinterpret_cast<const uint4*>(rows_ptr(p, e / p.El, p.y_off, p.rank, slot));
+              u[0][j] = kb::ld_sys_v4(row + vb);
+              if (vb + blockDim.x < v1) u[1][j] = kb::ld_sys_v4(row + vb + blockDim.x);
             }
           }
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float f[Vec16<T>::N];
-          Vec16<T>::load(u[j], f);
+        for (int b = 0; b < 2; ++b) {
 #pragma unroll
-          for (int i = 0; i < Vec16<T>::N; ++i) acc[i] = fmaf(wk[j], f[i], acc[i]);
+          for (int j = 0; j < 8; ++j) {
+            float f[Vec16<T>::N];
+            Vec16<T>::load(u[b][j], f);
+#pragma unroll
+            for (int i = 0; i < Vec16<T>::N; ++i) acc[b][i] = fmaf(wk[j], f[i], acc[b][i]);
+          }
         }
       }
-      reinterpret_cast<uint4*>(p.out + static_cast<size_t>(t) * p.row_bytes)[v] = Vec16<T>::store(acc);
+      uint4* orow = reinterpret_cast<uint4*>(p.out + static_cast<size_t>(t) * p.row_bytes);
+      orow[vb] = Vec16<T>::store(acc[0]);
+      if (vb + blockDim.x < v1) orow[vb + blockDim.x] = Vec16<T>::store(acc[1]);
     }
   }
   stamp(p, ST_DONE);
@@ -407,28 +517,35 @@ __device__ __forceinline__ void combine_body(const A2aParams& p) {
 
 template <typename T>
 __global__ void __launch_bounds__(A2A_THREADS) a2a_combine_kernel(const A2aParams p) {
-  combine_body<T>(p);
+  combine_body<T, false>(p);
 }
 
-// All three phases in one cooperative launch: the phases are separated only by
-// the epoch flags (this rank's own flag doubles as the grid-wide barrier), so
-// the two extra launches and their gaps disappear.  Needs every CTA resident,
-// which the cooperative launch guarantees.
+// All three phases in one cooperative launch (every CTA is resident, so CTAs may
+// wait for one another).  The last CTA of the grid is the poller: it moves no
+// rows, it is the only reader of the flag lines the peers write and republishes
+// them locally.  The other CTAs are the data CTAs; their phases are separated
+// only by the arrival words, this rank's own flags doubling as grid barrier.
 template <typename T>
 __global__ void __launch_bounds__(A2A_THREADS) a2a_fused_kernel(const A2aParams p) {
   extern __shared__ int32_t sh[];
-  dispatch_body(p, sh);
+  const int nworkers = static_cast<int>(gridDim.x) - 1;
+  if (static_cast<int>(blockIdx.x) == nworkers) {
+    poller_body(p);
+    return;
+  }
+  dispatch_body(p, sh, nworkers);
   __syncthreads();
-  expert_body<T>(p, sh);
+  expert_body<T, true>(p, sh, nworkers);
   __syncthreads();
-  combine_body<T>(p);
+  combine_body<T, true>(p);
 }
 
 // --------------------------------------------------------------- small utils ----
-__global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t want, uint64_t limit_ns, uint32_t* status) {
+__global__ void wait_flags_kernel(const uint32_t* flags, int n, int stride_words, uint32_t want, uint64_t limit_ns,
+                                  uint32_t* status) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
-    if (!kb::wait_flag_ge(flags + i, want, limit_ns)) {
+    if (!kb::wait_flag_ge(flags + static_cast<size_t>(i) * stride_words, want, limit_ns)) {
       kb::report_status(status, KB_DEV_TIMEOUT_FLAG, 21u, (uint32_t)i, want);
     }
   }
@@ -450,6 +567,17 @@ __global__ void device_barrier_kernel(const BarrierParams bp, uint64_t pad_off, 
   }
 }
 
+// Tells every rank that this rank's expert outputs of `epoch` are in place
+// (phase-1 flag), for callers that ran their own expert computation between
+// kb_a2a_dispatch and kb_a2a_combine.
+__global__ void post_ready_kernel(const A2aParams p) {
+  const int i = threadIdx.x;
+  if (i < p.world) {
+    kb::fence_sys();
+    kb::st_release_sys_u32(flag_ptr(p, i, 1, p.rank), p.epoch);
+  }
+}
+
 int fill_params(const KbA2aArgs* a, A2aParams* p, int sms) {
   if (a == nullptr) return KB_ERR_ARG;
   if (a->world < 1 || a->world > KB_MAX_WORLD || a->rank < 0 || a->rank >= a->world) {
@@ -468,6 +596,12 @@ int fill_params(const KbA2aArgs* a, A2aParams* p, int sms) {
   const long long row_bytes = static_cast<long long>(a->hidden) * a->elem_bytes;
   if (a->hidden <= 0 || row_bytes % 16 != 0) {
     kb::set_error("a2a: hidden*elem_bytes=%lld must be a positive multiple of 16", row_bytes);
+    return KB_ERR_ARG;
+  }
+  auto misaligned = [](const void* q, uintptr_t to) { return (reinterpret_cast<uintptr_t>(q) & (to - 1)) != 0; };
+  if (misaligned(a->x, 16) || misaligned(a->out, 16) || misaligned(a->indices, 4) || misaligned(a->weights, 4) ||
+      misaligned(a->slots, 4)) {
+    kb::set_error("a2a: x and out must be 16-byte aligned, indices, weights and slots 4-byte aligned");
     return KB_ERR_ARG;
   }
   memset(p, 0, sizeof(*p));
@@ -503,18 +637,18 @@ int fill_params(const KbA2aArgs* a, A2aParams* p, int sms) {
   p->status = a->status;
   p->limit_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
   p->trace = a->trace;
-  // Work split: one unit per CTA, about two CTAs per SM.  Units are token
-  // groups; with few tokens every group is further split along the hidden
-  // dimension so that more SMs take part.
-  const int target = 2 * sms;
+  // Work split: one unit per CTA, about two CTAs per SM (two slots stay free:
+  // one for the poller CTA of the fused launch).  Units are token groups; with
+  // few tokens every group is further split along the hidden dimension so that
+  // more SMs take part.
+  const int target = 2 * sms - 2 > 1 ? 2 * sms - 2 : 1;
   const int T = p->T > 0 ? p->T : 1;
   int tg = T < target ? T : target;
-  const int min_tg = (T * p->k + MAX_ENT_PER_CTA - 1) / MAX_ENT_PER_CTA;
+  // A CTA ranks the (tokens per group) * k entries of its group in a buffer of
+  // MAX_ENT_PER_CTA words: the group count must keep ceil(T / tg) * k inside it.
+  const int max_tok_per = MAX_ENT_PER_CTA / p->k;  // k <= 64, so at least 32
+  const int min_tg = (T + max_tok_per - 1) / max_tok_per;
   if (tg < min_tg) tg = min_tg;
-  if (tg > T) {
-    kb::set_error("a2a: topk=%d too large for the per-CTA ranking buffer", p->k);
-    return KB_ERR_ARG;
-  }
   int hs = target / tg;
   if (hs < 1) hs = 1;
   const int max_hs = (p->vecs + 31) / 32;  // at least a warp's worth of vectors per unit
@@ -539,6 +673,10 @@ int device_sms(int* sms) {
 
 }  // namespace
 
+extern "C" uint64_t kb_a2a_flag_bytes(void) { return 2ull * KB_MAX_WORLD * FLAG_STRIDE_WORDS * 4; }
+extern "C" uint64_t kb_a2a_sync_bytes(void) { return 512; }
+extern "C" int kb_a2a_flag_stride_words(void) { return FLAG_STRIDE_WORDS; }
+
 extern "C" uint64_t kb_a2a_rows_bytes(int world, int max_tokens, int topk, int hidden, int elem_bytes) {
   const uint64_t b = (uint64_t)world * max_tokens * topk * hidden * elem_bytes;
   return (b + 255) / 256 * 256;
@@ -557,6 +695,18 @@ extern "C" int kb_a2a_dispatch(const KbA2aArgs* a, void* stream) {
   return KB_OK;
 }
 
+extern "C" int kb_a2a_post_ready(const KbA2aArgs* a, void* stream) {
+  int sms = 0;
+  int rc = device_sms(&sms);
+  if (rc != KB_OK) return rc;
+  A2aParams p;
+  rc = fill_params(a, &p, sms);
+  if (rc != KB_OK) return rc;
+  post_ready_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  KB_CUDA_OK(cudaGetLastError());
+  return KB_OK;
+}
+
 extern "C" int kb_a2a_expert_scale(const KbA2aArgs* a, void* stream) {
   int sms = 0;
   int rc = device_sms(&sms);
@@ -564,7 +714,7 @@ extern "C" int kb_a2a_expert_scale(const KbA2aArgs* a, void* stream) {
   A2aParams p;
   rc = fill_params(a, &p, sms);
   if (rc != KB_OK) return rc;
-  const size_t smem = (p.world * p.El + p.world) * sizeof(int32_t);
+  const size_t smem = p.El * sizeof(int32_t);
   const int grid = a->num_ctas > 0 ? a->num_ctas : 2 * sms;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (a->dtype) {
@@ -599,7 +749,7 @@ extern "C" int kb_a2a_combine(const KbA2aArgs* a, void* stream) {
 template <typename T>
 static int launch_fused(const A2aParams& p, int sms, cudaStream_t st) {
   const size_t smem_d = (3 * p.E + 2 * MAX_ENT_PER_CTA) * sizeof(int32_t);
-  const size_t smem_e = (p.world * p.El + p.world) * sizeof(int32_t);
+  const size_t smem_e = p.El * sizeof(int32_t);
   const size_t smem = smem_d > smem_e ? smem_d : smem_e;
   // The occupancy query costs microseconds of host time; its answer depends only
   // on the kernel instance and the shared-memory size.
@@ -611,7 +761,7 @@ static int launch_fused(const A2aParams& p, int sms, cudaStream_t st) {
     cached_smem = smem;
     cached_per_sm = per_sm;
   }
-  const int units = p.tok_groups * p.h_splits;
+  const int units = p.tok_groups * p.h_splits + 1;  // data CTAs and the poller
   if (per_sm < 1 || units > per_sm * sms) {
     kb::set_error("a2a fused: %d CTAs cannot be co-resident (%d per SM)", units, per_sm);
     return KB_ERR_UNSUPPORTED;
@@ -640,10 +790,12 @@ extern "C" int kb_a2a_round_trip(const KbA2aArgs* a, void* stream) {
   return KB_ERR_ARG;
 }
 
-extern "C" int kb_wait_flags(const uint32_t* flags, int n, uint32_t want, uint64_t limit_ns, uint32_t* status,
-                             void* stream) {
+extern "C" int kb_wait_flags(const uint32_t* flags, int n, int stride_words, uint32_t want, uint64_t limit_ns,
+                             uint32_t* status, void* stream) {
   if (n <= 0) return KB_OK;
-  wait_flags_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(flags, n, want, limit_ns, status);
+  if (stride_words < 1) return KB_ERR_ARG;
+  wait_flags_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(flags, n, stride_words, want, limit_ns,
+                                                                                   status);
   KB_CUDA_OK(cudaGetLastError());
   return KB_OK;
 }
@@ -663,6 +815,8 @@ extern "C" int kb_device_barrier(void* const* peer_bases, uint64_t pad_off, int 
 // See a2a_static.h.  The workspace lives in a file-scope device array; host code
 // must not pass the array's name to a kernel (on the host it is only a stand-in
 // for the symbol), so its device address is looked up once per device.
+#include <mutex>
+
 #include "a2a_static.h"
 
 static __device__ __align__(256) unsigned char g_a2a_static_scratch[KB_A2A_STATIC_BYTES];
@@ -673,6 +827,40 @@ struct StaticSlot {
   uint32_t epoch = 0;
 };
 StaticSlot g_static_slots[64];
+std::mutex g_static_mu;  // guards g_static_slots (address look-up and epoch numbering)
+
+// Layout inside the array (all offsets multiples of 256).
+constexpr uint64_t ST_RECV_OFF = 0;
+constexpr uint64_t ST_Y_OFF = KB_A2A_STATIC_ROW_BYTES;
+constexpr uint64_t ST_SLOTS_OFF = 2ull * KB_A2A_STATIC_ROW_BYTES;
+constexpr uint64_t ST_COUNT_OFF = ST_SLOTS_OFF + 4ull * KB_A2A_STATIC_MAX_ROWS;
+constexpr uint64_t ST_FLAG_OFF = ST_COUNT_OFF + 4ull * KB_A2A_STATIC_MAX_EXPERTS;
+constexpr uint64_t ST_SYNC_OFF = ST_FLAG_OFF + 2ull * KB_MAX_WORLD * FLAG_STRIDE_WORDS * 4;
+constexpr uint64_t ST_STATUS_OFF = ST_SYNC_OFF + 512;
+static_assert(ST_STATUS_OFF + 256 <= KB_A2A_STATIC_BYTES, "static workspace layout exceeds the array");
+
+// Device index and workspace address of the current device (set-up on first use).
+int static_slot(int* dev_out, unsigned char** base_out, bool next_epoch, uint32_t* epoch_out) {
+  int dev = 0;
+  KB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    kb::set_error("a2a static: device index %d out of range", dev);
+    return KB_ERR_ARG;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  StaticSlot& slot = g_static_slots[dev];
+  if (slot.base == nullptr) {
+    // Set-up, once per device, with that device current.
+    unsigned char* ptr = nullptr;
+    KB_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_a2a_static_scratch));
+    slot.base = ptr;
+  }
+  if (next_epoch) ++slot.epoch;  // flags keep the previous call's epoch; epochs only grow
+  if (epoch_out != nullptr) *epoch_out = slot.epoch;
+  *dev_out = dev;
+  *base_out = slot.base;
+  return KB_OK;
+}
 }  // namespace
 
 extern "C" int kb_a2a_round_trip_static(const void* x, const int32_t* indices, const float* weights, void* out,
@@ -697,32 +885,16 @@ extern "C" int kb_a2a_round_trip_static(const void* x, const int32_t* indices, c
     return KB_ERR_ARG;
   }
   int dev = 0;
-  KB_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) {
-    kb::set_error("a2a static: device index %d out of range", dev);
-    return KB_ERR_ARG;
-  }
-  StaticSlot& slot = g_static_slots[dev];
-  if (slot.base == nullptr) {
-    // Set-up, once per device, with that device current.
-    unsigned char* ptr = nullptr;
-    KB_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_a2a_static_scratch));
-    slot.base = ptr;
-  }
+  unsigned char* base = nullptr;
+  uint32_t epoch = 0;
+  int rc = static_slot(&dev, &base, true, &epoch);
+  if (rc != KB_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  // Layout inside the array (all offsets multiples of 256).
-  const uint64_t recv_off = 0;
-  const uint64_t y_off = KB_A2A_STATIC_ROW_BYTES;
-  const uint64_t slots_off = 2ull * KB_A2A_STATIC_ROW_BYTES;
-  const uint64_t count_off = slots_off + 4ull * KB_A2A_STATIC_MAX_ROWS;
-  const uint64_t flag_off = count_off + 4ull * KB_A2A_STATIC_MAX_EXPERTS;
-  const uint64_t sync_off = flag_off + 256;
-  const uint64_t status_off = sync_off + 256;
-
   // The block counters must start at zero (a call that was cut short could have
-  // left them elsewhere); the status words are cleared for this call.
-  KB_CUDA_OK(cudaMemsetAsync(slot.base + sync_off, 0, 512, st));
+  // left them elsewhere).  The status words are NOT cleared here: a failure stays
+  // readable through kb_a2a_static_status until that call clears it.
+  KB_CUDA_OK(cudaMemsetAsync(base + ST_SYNC_OFF, 0, 512, st));
 
   KbA2aArgs a;
   memset(&a, 0, sizeof(a));
@@ -739,20 +911,35 @@ extern "C" int kb_a2a_round_trip_static(const void* x, const int32_t* indices, c
   a.indices = indices;
   a.weights = weights;
   a.out = out;
-  a.slots = reinterpret_cast<int32_t*>(slot.base + slots_off);
-  a.epoch = ++slot.epoch;  // flags keep the previous call's epoch; epochs only grow
-  a.peer_base[0] = slot.base;
-  a.recv_off = recv_off;
-  a.y_off = y_off;
-  a.count_off = count_off;
-  a.flag_off = flag_off;
-  a.sync_off = sync_off;
+  a.slots = reinterpret_cast<int32_t*>(base + ST_SLOTS_OFF);
+  a.epoch = epoch;
+  a.peer_base[0] = base;
+  a.recv_off = ST_RECV_OFF;
+  a.y_off = ST_Y_OFF;
+  a.count_off = ST_COUNT_OFF;
+  a.flag_off = ST_FLAG_OFF;
+  a.sync_off = ST_SYNC_OFF;
   a.scale_mode = scale_mode;
-  a.status = reinterpret_cast<uint32_t*>(slot.base + status_off);
+  a.status = reinterpret_cast<uint32_t*>(base + ST_STATUS_OFF);
   a.wait_limit_ns = 2000000000ull;
-  int rc = kb_a2a_dispatch(&a, st);
+  rc = kb_a2a_dispatch(&a, st);
   if (rc != KB_OK) return rc;
   rc = kb_a2a_expert_scale(&a, st);
   if (rc != KB_OK) return rc;
   return kb_a2a_combine(&a, st);
+}
+
+extern "C" int kb_a2a_static_status(uint32_t* out8, int clear, void* stream) {
+  if (out8 == nullptr) {
+    kb::set_error("a2a static: status destination is null");
+    return KB_ERR_ARG;
+  }
+  int dev = 0;
+  unsigned char* base = nullptr;
+  int rc = static_slot(&dev, &base, false, nullptr);
+  if (rc != KB_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  KB_CUDA_OK(cudaMemcpyAsync(out8, base + ST_STATUS_OFF, 8 * sizeof(uint32_t), cudaMemcpyDefault, st));
+  if (clear) KB_CUDA_OK(cudaMemsetAsync(base + ST_STATUS_OFF, 0, 8 * sizeof(uint32_t), st));
+  return KB_OK;
 }

@@ -29,6 +29,12 @@
 //     itself, on the given stream.  Two calls that overlap on the GPU (different
 //     streams, no dependency between them) race on the array: order them.
 //   * No cudaMalloc, cudaFree or allocating library routine is called.
+//   * The kernels check what they are given (expert ids in range, slots inside
+//     the workspace) and skip what fails the check instead of writing it.  Such a
+//     call still returns KB_OK, because the check runs on the GPU after the call
+//     has returned: read the device status words with kb_a2a_static_status once
+//     the stream has been synchronised.  The words keep the first failure until
+//     they are cleared.
 #pragma once
 #include <stdint.h>
 
@@ -39,7 +45,8 @@ extern "C" {
 #define KB_A2A_STATIC_ROW_BYTES (4u << 20)   // per region; there are two regions
 #define KB_A2A_STATIC_MAX_ROWS 16384
 #define KB_A2A_STATIC_MAX_EXPERTS 1024
-#define KB_A2A_STATIC_BYTES (2u * KB_A2A_STATIC_ROW_BYTES + 4u * KB_A2A_STATIC_MAX_ROWS + 4u * KB_A2A_STATIC_MAX_EXPERTS + 1024u)
+// two row regions, the slot table, the per-expert counts, 4 KB of flag lines, 512 bytes of counters, 256 of status
+#define KB_A2A_STATIC_BYTES (2u * KB_A2A_STATIC_ROW_BYTES + 4u * KB_A2A_STATIC_MAX_ROWS + 4u * KB_A2A_STATIC_MAX_EXPERTS + 4096u + 512u + 256u)
 
 // out[t] = sum_k weights[t,k] * scale(indices[t,k]) * x[t], the rows travelling
 // through the dispatch, expert and combine kernels exactly as in
@@ -48,6 +55,15 @@ extern "C" {
 // 2 (expert + 1) / num_experts.  Returns a KbStatus; see kb_last_error().
 int kb_a2a_round_trip_static(const void* x, const int32_t* indices, const float* weights, void* out, int num_tokens,
                              int num_experts, int topk, int hidden, int dtype, int scale_mode, void* stream);
+
+
+// Copies the eight device status words of the built-in workspace of the current
+// device to `out8` (host or device memory; pinned host memory keeps the copy
+// asynchronous) on `stream`, and with `clear` non-zero zeroes them afterwards.
+// out8[0] is a KbDevCode (0 = healthy, 3 = an index check rejected something),
+// out8[1] the site, out8[2] the offending entry, out8[3] the call's sequence
+// number, out8[4] the CTA.  Allocates nothing.  Returns a KbStatus.
+int kb_a2a_static_status(uint32_t* out8, int clear, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,23 +1,32 @@
-// Persistent, warp-specialised bf16 GEMM for sm_100a with three epilogues:
+// Persistent, warp-specialised bf16 GEMM for sm_100a in three modes:
 //
 //   PLAIN  out = A * B^T (+ bias)
-//   RS     GEMM fused with reduce-scatter: every 128x256 tile is converted to
-//          bf16 as it retires and its rows are stored straight into the row
-//          owner's staging area over NVLink; the owner's own tiles run last
-//          and their epilogue sums the peers' partials in fp32, adds the bias
-//          and writes the output shard.  No collective library call, no
-//          second kernel.
+//   RS     GEMM fused with reduce-scatter.  Every rank computes its K-shard's
+//          partial product tile by tile into its OWN half of a parity-buffered
+//          [M, N] bf16 staging matrix in the symmetric heap and, per tile,
+//          releases an epoch flag on the rank that owns the tile's rows.  Four
+//          extra "reduce" warps per CTA walk the rows this rank owns in the order
+//          in which the tiles complete everywhere, wait for the flags of all
+//          ranks, pull the partials over NVLink (peer loads, or one
+//          multimem.ld_reduce per 16 bytes that lets the switch add them), add the
+//          bias and write the output shard.  The tensor-core pipeline never waits
+//          for a peer, and the reduction of block c overlaps the GEMM of block c+1:
+//          all ranks visit block c of every owner at about the same time.
 //   AG     all-gather fused with GEMM: extra "comm" warps of the same kernel
-//          stream this rank's A rows into every peer's gather buffer while the
+//          stream this rank's A rows into every peer's gather buffer (peer stores,
+//          or one multimem.st per 16 bytes that the switch replicates) while the
 //          tensor cores already work on the rows that are present; the TMA
 //          producer waits (bounded) on a per-row-block flag before it loads
 //          rows that come from a peer.
 //
-// Mainloop: one TMA producer thread fills a 4-stage ring of 128x64 (A) and
-// 256x64 (B) K-major tiles with 128-byte swizzle; one thread issues
-// tcgen05.mma (M128 N256 K16) into one of two 256-column TMEM accumulators;
-// four epilogue warps drain the other accumulator (tcgen05.ld -> bf16 ->
-// swizzled smem -> 16-byte row-contiguous global accesses).
+// Mainloop: one TMA producer thread fills a ring of 128x64 (A) and 256x64 (B)
+// K-major tiles with 128-byte swizzle; one thread issues tcgen05.mma into one of
+// two 256-column TMEM accumulators; four epilogue warps drain the other
+// accumulator.  PLAIN and AG write the output with TMA stores (tcgen05.ld ->
+// bf16 -> 128-byte-swizzled shared memory -> cp.async.bulk.tensor store issued
+// by one lane per warp, two staging buffers per warp); RS writes the staging
+// matrix with 16-byte row-contiguous stores, whose ordering against the flag
+// release is that of ordinary stores.
 //
 // The op replaces torch.matmul + bias add + reduce_scatter_tensor of the
 // reference (gemm_rs/reference.py:49-60, gemm_rs/submission.py:23-28).
@@ -52,20 +61,29 @@ struct Cfg {
   static constexpr int B_BYTES = B_ROWS * BK * 2;
 };
 constexpr int MAX_STAGES = 6;
-constexpr int EPI_COLS = 128;                 // columns staged per epilogue pass
-constexpr int EPI_ROW_BYTES = EPI_COLS * 2;   // 256
+// Epilogue staging: 8 KB per warp.  RS: 32 rows x 128 columns (256-byte rows,
+// 16-byte chunks XOR-swizzled by row).  PLAIN/AG: two buffers of 32 rows x 64
+// columns in the 128-byte-swizzle layout of the output tensor map.
+constexpr int EPI_COLS = 128;
+constexpr int EPI_ROW_BYTES = EPI_COLS * 2;
 constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;
 constexpr int EPI_BYTES = 4 * EPI_WARP_BYTES;
+constexpr int OUT_BOX_COLS = 64;
+constexpr int OUT_BOX_ROWS = 32;
+constexpr int OUT_BOX_BYTES = OUT_BOX_ROWS * OUT_BOX_COLS * 2;  // 4 KB
 constexpr int TMEM_COLS = 512;
 constexpr int BAR_BYTES = 256;
 constexpr int SMEM_BYTES = 1024 + 4 * (A_BYTES + 32768) + EPI_BYTES + BAR_BYTES;  // same total for both configurations
 constexpr int THREADS_BASE = 256;             // warps 0..3 control, 4..7 epilogue
-constexpr int THREADS_AG = 384;               // + warps 8..11 comm
+constexpr int THREADS_COMM = 384;             // + warps 8..11: all-gather pushers or reduce-scatter reducers
+constexpr int RS_ROW_GROUP = 64;              // rows of one reduction unit
+constexpr int RS_UNIT_COLS = 128;             // columns of one reduction unit
 
 struct alignas(64) GemmParams {
   CUtensorMap tmA;
   CUtensorMap tmB;
   CUtensorMap tmOwn;  // AG: this rank's own rows, read in place
+  CUtensorMap tmOut;  // PLAIN/AG: the output, written with TMA stores
   int mode, M, N, K;
   int MB, NB, KB;
   const bf16* bias;
@@ -74,18 +92,19 @@ struct alignas(64) GemmParams {
   int rank, world, rpo;
   uint32_t epoch;
   char* peer_base[KB_MAX_WORLD];
+  char* mc_base;  // multicast mapping of the heap, or null: peer loads / stores instead of multimem
   uint64_t data_off, flag_off, counter_off;
   const bf16* a_local;
   uint32_t* status;
   uint64_t limit_ns;
   int own_lo_mb, own_hi_mb;
-  int ag_parts;
   // Scheduling blocks: 128 rows (single CTA) or 256 rows (CTA pair).
-  int MBQ, own_lo_q, own_hi_q;
-  int group;  // scheduling blocks swept together (rasterisation)
+  int MBQ, own_lo_q;
+  int group;          // scheduling blocks swept together (rasterisation)
   int ag_own_direct;  // AG: own row blocks are loaded straight from the input (no self copy)
-  int ag_n_own;  // AG: scheduling blocks per source when they tile the rows evenly, else 0 (plain rotated order)
-  int debug;  // experiments only (KB200_GEMM_DEBUG): 1 no global stores, 2 epilogue only releases TMEM, 4 every load reads tile (0,0), 8 timing words: status[5] max us waited on peers, [6] us until the pushes were out, [7] us until the last epilogue
+  int ag_n_own;       // AG: scheduling blocks per source when they tile the rows evenly, else 0 (plain rotated order)
+  int rs_nq;          // RS: scheduling blocks per owner when they tile the rows evenly, else 0 (plain order)
+  int timing;         // record timing words: status[5] max us waited on peers, [6] us until the pushes were out, [7] us until the last epilogue / reduction ended
 };
 
 enum Site : uint32_t {
@@ -116,7 +135,7 @@ __device__ __forceinline__ Smem carve(uint8_t* raw) {
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   s.a = base;
   s.b = base + STAGES * A_BYTES;
-  s.epi = s.b + STAGES * Cfg<kPair>::B_BYTES;
+  s.epi = s.b + STAGES * Cfg<kPair>::B_BYTES;  // 1024-byte aligned: every stage is a multiple of 1024 bytes
   uint64_t* bars = reinterpret_cast<uint64_t*>(s.epi + EPI_BYTES);
   s.full = bars;
   s.empty = bars + MAX_STAGES;
@@ -129,142 +148,70 @@ __device__ __forceinline__ Smem carve(uint8_t* raw) {
 
 // Position in the static schedule -> tile coordinates.
 //
-// Row blocks are visited in a rank-rotated sequence: RS starts just after the
-// blocks this rank owns (so they come last and every owner is fed by a
-// different peer at any time); AG starts with this rank's own rows (which need
-// no transfer).  Inside the sequence, GROUP_M consecutive row blocks form a
-// group that is swept column block by column block, so that the ~148 tiles in
-// flight share few A and B panels (L2 reuse instead of HBM re-reads).  For RS
-// the blocks this rank owns form a segment of their own at the very end: a CTA
-// never has a push queued behind one of its own waits, which is what makes
-// the cross-rank waits deadlock-free.
-template <bool kPair>
+// Scheduling blocks are visited in a sequence that depends on the mode; groups
+// of GROUP_M consecutive sequence entries are swept column block by column
+// block, so that the ~148 tiles in flight share few A and B panels (L2 reuse
+// instead of HBM re-reads).
+//   PLAIN  ascending.
+//   RS     block c of every owner, then block c+1 of every owner, ... (owners in
+//          ring order after this rank): all ranks finish block c of an owner at
+//          about the same time, so its reduction overlaps the GEMM of block c+1.
+//   AG     this rank's own blocks (no transfer needed), then block c of every
+//          other source (nearest first) for c = 0, 1, ...: the order in which
+//          the pushes arrive.
 __host__ __device__ __forceinline__ void tile_at(const GemmParams& p, int pos, int& mbq, int& nb) {
   const int GROUP_M = p.group;
-  int start = 0;
-  int first_len = p.MBQ;  // blocks in the first segment
-  if (p.mode == KB_GEMM_RS) {
-    start = p.own_hi_q + 1;
-    first_len = p.MBQ - (p.own_hi_q - p.own_lo_q + 1);
-  }
-  if (p.mode == KB_GEMM_AG) start = p.own_lo_q;
-  if (p.mode == KB_GEMM_AG && p.ag_n_own > 0) {
-    // Own blocks first, then block c of every other source (nearest first) for
-    // c = 0, 1, ...: the order in which the pushes arrive.  Groups of GROUP_M
-    // consecutive sequence entries are swept column block by column block.
-    const int per_group = GROUP_M * p.NB;
-    const int g = pos / per_group;
-    const int r = pos - g * per_group;
-    int gs = p.MBQ - g * GROUP_M;
-    if (gs > GROUP_M) gs = GROUP_M;
-    nb = r / gs;
-    const int j = g * GROUP_M + (r - nb * gs);
-    if (j < p.ag_n_own) {
-      mbq = p.own_lo_q + j;
-    } else {
-      const int jj = j - p.ag_n_own;
-      const int c = jj / (p.world - 1);
-      const int d = jj - c * (p.world - 1) + 1;
-      mbq = ((p.rank + d) % p.world) * p.ag_n_own + c;
-    }
-    return;
-  }
-  int base = 0, blocks = first_len, q = pos;
-  if (pos >= first_len * p.NB) {
-    base = first_len;
-    blocks = p.MBQ - first_len;
-    q = pos - first_len * p.NB;
-  }
   const int per_group = GROUP_M * p.NB;
-  const int g = q / per_group;
-  const int r = q - g * per_group;
-  int gs = blocks - g * GROUP_M;
+  const int g = pos / per_group;
+  const int r = pos - g * per_group;
+  int gs = p.MBQ - g * GROUP_M;
   if (gs > GROUP_M) gs = GROUP_M;
   nb = r / gs;
-  const int j = base + g * GROUP_M + (r - nb * gs);
-  mbq = (start + j) % p.MBQ;
+  const int j = g * GROUP_M + (r - nb * gs);  // index in the block sequence
+  mbq = j;
+  if (p.mode == KB_GEMM_RS && p.rs_nq > 0) {
+    const int c = j / p.world;
+    const int o = (p.rank + 1 + (j - c * p.world)) % p.world;
+    mbq = o * p.rs_nq + c;
+  } else if (p.mode == KB_GEMM_AG) {
+    if (p.ag_n_own > 0) {
+      if (j < p.ag_n_own) {
+        mbq = p.own_lo_q + j;
+      } else {
+        const int jj = j - p.ag_n_own;
+        const int c = jj / (p.world - 1);
+        const int d = jj - c * (p.world - 1) + 1;
+        mbq = ((p.rank + d) % p.world) * p.ag_n_own + c;
+      }
+    } else {
+      mbq = (p.own_lo_q + j) % p.MBQ;
+    }
+  }
 }
 
+// RS: flag of (source rank, tile) on the rank that owns rows of the tile.
 __device__ __forceinline__ uint32_t* rs_flag(const GemmParams& p, int on_rank, int src, int tile) {
   const uint32_t parity = p.epoch & 1u;
   uint32_t* base = reinterpret_cast<uint32_t*>(p.peer_base[on_rank] + p.flag_off);
   return base + (static_cast<size_t>(parity) * p.world + src) * (static_cast<size_t>(p.MB) * p.NB) + tile;
 }
-__device__ __forceinline__ bf16* rs_stage_row(const GemmParams& p, int on_rank, int src, int row_local) {
+// RS: element offset of row `row` of this epoch's [M, N] staging matrix inside a segment.
+__device__ __forceinline__ size_t rs_stage_elem(const GemmParams& p, int row) {
   const uint32_t parity = p.epoch & 1u;
-  bf16* base = reinterpret_cast<bf16*>(p.peer_base[on_rank] + p.data_off);
-  return base + ((static_cast<size_t>(parity) * p.world + src) * p.rpo + row_local) * static_cast<size_t>(p.N);
+  return (static_cast<size_t>(parity) * p.M + row) * static_cast<size_t>(p.N);
 }
 __device__ __forceinline__ uint32_t* ag_flag(const GemmParams& p, int on_rank, int src, int mb) {
   const uint32_t parity = p.epoch & 1u;
   uint32_t* base = reinterpret_cast<uint32_t*>(p.peer_base[on_rank] + p.flag_off);
   return base + (static_cast<size_t>(parity) * p.world + src) * p.MB + mb;
 }
-__device__ __forceinline__ bf16* ag_gather_row(const GemmParams& p, int on_rank, int row) {
+__device__ __forceinline__ size_t ag_gather_elem(const GemmParams& p, int row) {
   const uint32_t parity = p.epoch & 1u;
-  bf16* base = reinterpret_cast<bf16*>(p.peer_base[on_rank] + p.data_off);
-  return base + (static_cast<size_t>(parity) * p.M + row) * static_cast<size_t>(p.K);
+  return (static_cast<size_t>(parity) * p.M + row) * static_cast<size_t>(p.K);
 }
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void comm_bar_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
-
-// TMEM -> bf16 -> this warp's 32 x 128 staging rows (16-byte chunks XOR-swizzled
-// by row so both the row-per-thread writes and the row-contiguous reads are
-// bank-conflict free).
-__device__ __forceinline__ void stage_half(uint32_t taddr, uint8_t* warp_epi, int lane, const bf16* bias = nullptr,
-                                           float bias_scale = 1.f, int col0 = 0, int n_cols = 0) {
-#pragma unroll
-  for (int c = 0; c < EPI_COLS / 32; ++c) {
-    uint32_t r[32];
-    kb::tmem_ld_32x32(taddr + c * 32, r);
-    kb::tmem_ld_wait();
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float f[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * i + e]);
-      if (bias != nullptr) {
-        // Added in fp32 before the single rounding to bf16.  All lanes read
-        // the same 16 bytes (they hold different rows of the same columns).
-        const int col = col0 + c * 32 + i * 8;
-        if (col < n_cols) {
-          const uint4 bv = *reinterpret_cast<const uint4*>(bias + col);
-          float2 t;
-          t = kb::unpack_bf16x2(bv.x); f[0] += bias_scale * t.x; f[1] += bias_scale * t.y;
-          t = kb::unpack_bf16x2(bv.y); f[2] += bias_scale * t.x; f[3] += bias_scale * t.y;
-          t = kb::unpack_bf16x2(bv.z); f[4] += bias_scale * t.x; f[5] += bias_scale * t.y;
-          t = kb::unpack_bf16x2(bv.w); f[6] += bias_scale * t.x; f[7] += bias_scale * t.y;
-        }
-      }
-      uint4 v;
-      v.x = kb::pack_bf16x2(f[0], f[1]);
-      v.y = kb::pack_bf16x2(f[2], f[3]);
-      v.z = kb::pack_bf16x2(f[4], f[5]);
-      v.w = kb::pack_bf16x2(f[6], f[7]);
-      const int j = c * 4 + i;
-      const int phys = j ^ (lane & 15);
-      *reinterpret_cast<uint4*>(warp_epi + lane * EPI_ROW_BYTES + phys * 16) = v;
-    }
-  }
-}
-
-// TMEM -> fp32 -> this warp's 32 x 64 staging rows (256 bytes per row, same XOR
-// swizzle of the 16-byte chunks).
-__device__ __forceinline__ void stage_quarter_f32(uint32_t taddr, uint8_t* warp_epi, int lane) {
-#pragma unroll
-  for (int c = 0; c < 2; ++c) {
-    uint32_t r[32];
-    kb::tmem_ld_32x32(taddr + c * 32, r);
-    kb::tmem_ld_wait();
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint4 v = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-      const int j = c * 8 + i;
-      *reinterpret_cast<uint4*>(warp_epi + lane * EPI_ROW_BYTES + ((j ^ (lane & 15)) * 16)) = v;
-    }
-  }
-}
 
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
   float2 t;
@@ -281,15 +228,60 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   o.w = kb::pack_bf16x2(f[6], f[7]);
   return o;
 }
-__device__ __forceinline__ void load_bias8(const bf16* b, float scale, float* out) {
-  const uint4 bv = *reinterpret_cast<const uint4*>(b);
-  unpack8(bv, out);
+
+// Eight fp32 accumulator values (+ bias, added in fp32 before the single rounding) -> eight bf16.
+__device__ __forceinline__ uint4 cvt8(const uint32_t* r, const bf16* bias, float bias_scale, int col, int n_cols) {
+  float f[8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) out[e] *= scale;
+  for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[e]);
+  if (bias != nullptr && col < n_cols) {
+    // All lanes read the same 16 bytes (they hold different rows of the same columns).
+    float b[8];
+    unpack8(*reinterpret_cast<const uint4*>(bias + col), b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] += bias_scale * b[e];
+  }
+  return pack8(f);
+}
+
+// TMEM -> bf16 -> this warp's 32 x 128 staging rows (16-byte chunks XOR-swizzled
+// by row so both the row-per-thread writes and the row-contiguous reads are
+// bank-conflict free).
+__device__ __forceinline__ void stage_half(uint32_t taddr, uint8_t* warp_epi, int lane) {
+#pragma unroll
+  for (int c = 0; c < EPI_COLS / 32; ++c) {
+    uint32_t r[32];
+    kb::tmem_ld_32x32(taddr + c * 32, r);
+    kb::tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = cvt8(r + 8 * i, nullptr, 0.f, 0, 0);
+      const int j = c * 4 + i;
+      *reinterpret_cast<uint4*>(warp_epi + lane * EPI_ROW_BYTES + ((j ^ (lane & 15)) * 16)) = v;
+    }
+  }
+}
+
+// TMEM -> bf16 (+ bias) -> one 32 x 64 box in the 128-byte-swizzle layout of the
+// output tensor map: row = lane, 16-byte chunk j of the row at position j ^ (row & 7).
+__device__ __forceinline__ void stage_box(uint32_t taddr, uint8_t* box, int lane, const bf16* bias, float bias_scale,
+                                          int col0, int n_cols) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t r[32];
+    kb::tmem_ld_32x32(taddr + c * 32, r);
+    kb::tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int j = c * 4 + i;
+      const uint4 v = cvt8(r + 8 * i, bias, bias_scale, col0 + j * 8, n_cols);
+      *reinterpret_cast<uint4*>(box + lane * (OUT_BOX_COLS * 2) + ((j ^ (lane & 7)) * 16)) = v;
+    }
+  }
 }
 
 template <int kMode, bool kPair>
-__global__ void __launch_bounds__(kMode == KB_GEMM_AG ? THREADS_AG : THREADS_BASE, 1)
+__global__ void __launch_bounds__(kMode == KB_GEMM_PLAIN ? THREADS_BASE : THREADS_COMM, 1)
 gemm_kernel(const __grid_constant__ GemmParams p) {
   constexpr bool kAG = (kMode == KB_GEMM_AG);
   constexpr bool kRS = (kMode == KB_GEMM_RS);
@@ -307,7 +299,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int total_tiles = p.MBQ * p.NB;
-  const uint64_t t_start = kb::globaltimer_ns();  // for the optional timing words status[5..7]
+  const uint64_t t_start = p.timing ? kb::globaltimer_ns() : 0;
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -334,6 +326,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     kb::tma_prefetch_desc(&p.tmA);
     kb::tma_prefetch_desc(&p.tmB);
     if (kAG && p.ag_own_direct) kb::tma_prefetch_desc(&p.tmOwn);
+    if (!kRS) kb::tma_prefetch_desc(&p.tmOut);
   }
   kb::tc_fence_before_sync();
   __syncthreads();
@@ -351,7 +344,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       bool ok = true;
       for (int pos = sched_id; pos < total_tiles && ok; pos += sched_n) {
         int mbq, nb;
-        tile_at<kPair>(p, pos, mbq, nb);
+        tile_at(p, pos, mbq, nb);
         const int mb = kPair ? 2 * mbq + static_cast<int>(cta_rank) : mbq;
         const bool own_direct = kAG && p.ag_own_direct && mb >= p.own_lo_mb && mb <= p.own_hi_mb;
         const CUtensorMap* map_a = own_direct ? &p.tmOwn : &p.tmA;
@@ -361,13 +354,13 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           int last_row = mb * BM + BM - 1;
           if (last_row > p.M - 1) last_row = p.M - 1;
           const int s_hi = last_row / p.rpo;
-          const uint64_t w0 = kb::globaltimer_ns();
+          const uint64_t w0 = p.timing ? kb::globaltimer_ns() : 0;
           for (int src = s_lo; src <= s_hi; ++src) {
             if (!kb::wait_flag_ge(ag_flag(p, p.rank, src, mb), p.epoch, p.limit_ns)) {
               kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_AG_FLAG, (uint32_t)src, p.epoch);
             }
           }
-          waited_ns += kb::globaltimer_ns() - w0;
+          if (p.timing) waited_ns += kb::globaltimer_ns() - w0;
           kb::fence_proxy_async_global();
           if (mb < 256) ready_mask[mb >> 6] |= 1ull << (mb & 63);
         }
@@ -383,12 +376,12 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
             // leader's barrier, which expects the sum.
             const uint32_t bar = kb::map_to_cta(kb::smem_u32(&sm.full[s]), 0u);
             if (leader) kb::mbar_arrive_expect_tx(&sm.full[s], 2 * (A_BYTES + B_BYTES));
-            kb::tma_load_2d_pair(sm.a + s * A_BYTES, map_a, bar, (p.debug & 4) ? 0 : kb_i * BK, (p.debug & 4) ? 0 : a_row);
-            kb::tma_load_2d_pair(sm.b + s * B_BYTES, &p.tmB, bar, (p.debug & 4) ? 0 : kb_i * BK, (p.debug & 4) ? 0 : nb * BN + static_cast<int>(cta_rank) * 128);
+            kb::tma_load_2d_pair(sm.a + s * A_BYTES, map_a, bar, kb_i * BK, a_row);
+            kb::tma_load_2d_pair(sm.b + s * B_BYTES, &p.tmB, bar, kb_i * BK, nb * BN + static_cast<int>(cta_rank) * 128);
           } else {
             kb::mbar_arrive_expect_tx(&sm.full[s], A_BYTES + B_BYTES);
-            kb::tma_load_2d(sm.a + s * A_BYTES, map_a, &sm.full[s], (p.debug & 4) ? 0 : kb_i * BK, (p.debug & 4) ? 0 : a_row);
-            kb::tma_load_2d(sm.b + s * B_BYTES, &p.tmB, &sm.full[s], (p.debug & 4) ? 0 : kb_i * BK, (p.debug & 4) ? 0 : nb * BN);
+            kb::tma_load_2d(sm.a + s * A_BYTES, map_a, &sm.full[s], kb_i * BK, a_row);
+            kb::tma_load_2d(sm.b + s * B_BYTES, &p.tmB, &sm.full[s], kb_i * BK, nb * BN);
           }
           if (++s == STAGES) {
             s = 0;
@@ -396,7 +389,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           }
         }
       }
-      if (kAG && p.status != nullptr && (p.debug & 8)) atomicMax(&p.status[5], static_cast<uint32_t>(waited_ns / 1000));
+      if (kAG && p.status != nullptr && p.timing) atomicMax(&p.status[5], static_cast<uint32_t>(waited_ns / 1000));
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -467,22 +460,24 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     const int q = warp - 4;
     const int et = tid - 128;
     uint8_t* warp_epi = sm.epi + q * EPI_WARP_BYTES;
-    constexpr bool rs = kRS;  // the host maps single-rank calls to the plain kernel
     uint32_t it = 0;
-    uint64_t rs_waited_ns = 0;
     // Releases this CTA's share of the accumulator: locally for the leader, on
     // the leader's barrier for its partner.
     auto release_acc = [&](uint32_t acc) {
-      if constexpr (kPair) {
-        if (leader) kb::mbar_arrive(&sm.tempty[acc]);
-        else kb::mbar_arrive_cluster(kb::map_to_cta(kb::smem_u32(&sm.tempty[acc]), 0u));
-      } else {
-        kb::mbar_arrive(&sm.tempty[acc]);
+      kb::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kPair) {
+          if (leader) kb::mbar_arrive(&sm.tempty[acc]);
+          else kb::mbar_arrive_cluster(kb::map_to_cta(kb::smem_u32(&sm.tempty[acc]), 0u));
+        } else {
+          kb::mbar_arrive(&sm.tempty[acc]);
+        }
       }
     };
     for (int pos = sched_id; pos < total_tiles; pos += sched_n, ++it) {
       int mbq, nb;
-      tile_at<kPair>(p, pos, mbq, nb);
+      tile_at(p, pos, mbq, nb);
       const int mb = kPair ? 2 * mbq + static_cast<int>(cta_rank) : mbq;
       const uint32_t acc = it & 1u;
       const uint32_t aph = (it >> 1) & 1u;
@@ -495,177 +490,167 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       kb::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
       const int row0 = mb * BM;
-      int last_row = row0 + BM - 1;
-      if (last_row > p.M - 1) last_row = p.M - 1;
-      int o_lo = 0, o_hi = 0;
-      bool has_remote = false, has_own = true;
-      if (rs && row0 < p.M) {
-        o_lo = row0 / p.rpo;
-        o_hi = last_row / p.rpo;
-        has_own = (p.rank >= o_lo && p.rank <= o_hi);
-        has_remote = !(o_lo == p.rank && o_hi == p.rank);
-      }
-      const int tile_id = mb * p.NB + nb;
-      bool released = false;
-      if (p.debug & 2) {
-        kb::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) release_acc(acc);
-        continue;
-      }
 
-      if (kRS && has_remote) {
-        // Phase A: rows that belong to other ranks go to their owners.
+      if constexpr (!kRS) {
+        // Four passes of 64 columns through two staging boxes; lane 0 owns the
+        // bulk groups of this warp.  A box is rewritten only after the store that
+        // last read it has finished reading (at most one younger group pending).
+        const int gr0 = row0 + q * 32;
+#pragma unroll 1
+        for (int ps = 0; ps < BN / OUT_BOX_COLS; ++ps) {
+          uint8_t* box = warp_epi + (ps & 1) * OUT_BOX_BYTES;
+          if (lane == 0) kb::bulk_wait_group_read<1>();
+          __syncwarp();
+          const int col0 = nb * BN + ps * OUT_BOX_COLS;
+          stage_box(taddr + ps * OUT_BOX_COLS, box, lane, p.bias, p.bias_scale, col0, p.N);
+          if (ps == BN / OUT_BOX_COLS - 1) release_acc(acc);
+          kb::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (gr0 < p.M && col0 < p.N) kb::tma_store_2d(&p.tmOut, box, col0, gr0);
+            kb::bulk_commit_group();  // also when nothing was stored: one group per pass keeps the count simple
+          }
+        }
+      } else {
+        // Reduce-scatter: the whole tile goes, as bf16, into this rank's own
+        // staging matrix; then the owners of its rows are told.
+        bf16* stage = reinterpret_cast<bf16*>(p.peer_base[p.rank] + p.data_off);
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
           stage_half(taddr + h * EPI_COLS, warp_epi, lane);
-          if (h == 1 && !has_own) {
-            kb::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) release_acc(acc);
-            released = true;
-          }
+          if (h == 1) release_acc(acc);
           __syncwarp();
+          const int j = lane & 15;
+          const int col = nb * BN + h * EPI_COLS + j * 8;
 #pragma unroll 4
           for (int i = 0; i < 16; ++i) {
             const int row = i * 2 + (lane >> 4);
-            const int j = lane & 15;
             const int gr = row0 + q * 32 + row;
-            const int col = nb * BN + h * EPI_COLS + j * 8;
             if (gr < p.M && col < p.N) {
-              const int owner = gr / p.rpo;
-              if (owner != p.rank) {
-                const uint4 v = *reinterpret_cast<const uint4*>(warp_epi + row * EPI_ROW_BYTES + ((j ^ (row & 15)) * 16));
-                bf16* dst = rs_stage_row(p, owner, p.rank, gr - owner * p.rpo) + col;
-                kb::st_sys_v4(dst, v);
-              }
+              const uint4 v = *reinterpret_cast<const uint4*>(warp_epi + row * EPI_ROW_BYTES + ((j ^ (row & 15)) * 16));
+              *reinterpret_cast<uint4*>(stage + rs_stage_elem(p, gr) + col) = v;
             }
           }
           __syncwarp();
         }
         epi_bar_sync();
-        if (et == 0) {
+        if (et == 0 && row0 < p.M) {
+          int last_row = row0 + BM - 1;
+          if (last_row > p.M - 1) last_row = p.M - 1;
+          const int tile_id = mb * p.NB + nb;
           kb::fence_sys();
-          for (int o = o_lo; o <= o_hi; ++o) {
-            if (o != p.rank) kb::st_release_sys_u32(rs_flag(p, o, p.rank, tile_id), p.epoch);
-          }
+          for (int o = row0 / p.rpo; o <= last_row / p.rpo; ++o) kb::st_relaxed_sys_u32(rs_flag(p, o, p.rank, tile_id), p.epoch);
         }
-      }
-
-      if (has_own) {
-        if (rs) {
-          if (et < p.world && et != p.rank) {
-            const uint64_t w0 = kb::globaltimer_ns();
-            if (!kb::wait_flag_ge(rs_flag(p, p.rank, et, tile_id), p.epoch, p.limit_ns)) {
-              kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_RS_FLAG, (uint32_t)et, p.epoch);
-            }
-            rs_waited_ns += kb::globaltimer_ns() - w0;
-          }
-          epi_bar_sync();
-        }
-        if constexpr (!kRS) {
-#pragma unroll 1
-          for (int h = 0; h < 2; ++h) {
-            stage_half(taddr + h * EPI_COLS, warp_epi, lane, p.bias, p.bias_scale, nb * BN + h * EPI_COLS, p.N);
-            if (h == 1) {
-              kb::tc_fence_before_sync();
-              __syncwarp();
-              if (lane == 0) release_acc(acc);
-              released = true;
-            }
-            __syncwarp();
-            const int j = lane & 15;
-            const int col = nb * BN + h * EPI_COLS + j * 8;
-#pragma unroll 4
-            for (int i = 0; i < 16; ++i) {
-              const int row = i * 2 + (lane >> 4);
-              const int gr = row0 + q * 32 + row;
-              if (gr < p.M && col < p.N && !(p.debug & 1)) {
-                const uint4 v = *reinterpret_cast<const uint4*>(warp_epi + row * EPI_ROW_BYTES + ((j ^ (row & 15)) * 16));
-                *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(gr) * p.N + col) = v;
-              }
-            }
-            __syncwarp();
-          }
-        } else {
-          // Own rows of a reduce-scatter tile.  The local accumulator stays in
-          // fp32 (staged 64 columns at a time); the peers' bf16 partials are
-          // added in ascending source order, so the sum is bit-reproducible.
-          // Loads are issued in batches of 8 rows x 4 sources per thread so
-          // that enough of them are in flight to cover the memory latency.
-#pragma unroll 1
-          for (int qd = 0; qd < 4; ++qd) {
-            stage_quarter_f32(taddr + qd * 64, warp_epi, lane);
-            if (qd == 3) {
-              kb::tc_fence_before_sync();
-              __syncwarp();
-              if (lane == 0) release_acc(acc);
-              released = true;
-            }
-            __syncwarp();
-            const int c8 = lane & 7;
-            const int col = nb * BN + qd * 64 + c8 * 8;
-            float accv[8][8];
-            int out_rows[8];
-#pragma unroll
-            for (int ii = 0; ii < 8; ++ii) {
-              const int row = ii * 4 + (lane >> 3);
-              const int gr = row0 + q * 32 + row;
-              const bool mine = (gr < p.M) && (col < p.N) && (gr / p.rpo == p.rank);
-              out_rows[ii] = mine ? gr - p.rank * p.rpo : -1;
-              const uint8_t* rowp = warp_epi + row * EPI_ROW_BYTES;
-              const float4 lo = *reinterpret_cast<const float4*>(rowp + (((2 * c8) ^ (row & 15)) * 16));
-              const float4 hi = *reinterpret_cast<const float4*>(rowp + (((2 * c8 + 1) ^ (row & 15)) * 16));
-              accv[ii][0] = lo.x; accv[ii][1] = lo.y; accv[ii][2] = lo.z; accv[ii][3] = lo.w;
-              accv[ii][4] = hi.x; accv[ii][5] = hi.y; accv[ii][6] = hi.z; accv[ii][7] = hi.w;
-            }
-#pragma unroll 1
-            for (int s0 = 0; s0 < p.world; s0 += 4) {
-              uint4 u[8][4];
-#pragma unroll
-              for (int ii = 0; ii < 8; ++ii) {
-#pragma unroll
-                for (int sj = 0; sj < 4; ++sj) {
-                  const int src = s0 + sj;
-                  u[ii][sj] = make_uint4(0u, 0u, 0u, 0u);
-                  if (out_rows[ii] >= 0 && src < p.world && src != p.rank) {
-                    u[ii][sj] = kb::ld_sys_v4(rs_stage_row(p, p.rank, src, out_rows[ii]) + col);
-                  }
-                }
-              }
-#pragma unroll
-              for (int ii = 0; ii < 8; ++ii) {
-#pragma unroll
-                for (int sj = 0; sj < 4; ++sj) {
-                  float f[8];
-                  unpack8(u[ii][sj], f);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) accv[ii][e] += f[e];
-                }
-              }
-            }
-            float bz[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (p.bias != nullptr && col < p.N) load_bias8(p.bias + col, p.bias_scale, bz);
-#pragma unroll
-            for (int ii = 0; ii < 8; ++ii) {
-              if (out_rows[ii] >= 0) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) accv[ii][e] += bz[e];
-                *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(out_rows[ii]) * p.N + col) = pack8(accv[ii]);
-              }
-            }
-            __syncwarp();
-          }
-        }
-      }
-      if (!released) {
-        kb::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) release_acc(acc);
       }
     }
-    if (p.status != nullptr && (p.debug & 8) && lane == 0) {
-      if (kRS) atomicMax(&p.status[5], static_cast<uint32_t>(rs_waited_ns / 1000));
+    if constexpr (!kRS) {
+      if (lane == 0) kb::bulk_wait_group<0>();  // the staging boxes are read and the output is written before the CTA leaves
+    }
+    if (p.status != nullptr && p.timing && lane == 0 && !kRS) {
+      atomicMax(&p.status[7], static_cast<uint32_t>((kb::globaltimer_ns() - t_start) / 1000));
+    }
+  } else if (kRS && warp >= 8) {
+    // ------------------------------------------------ reduce-scatter reducer ----
+    // Units of 64 rows x 128 columns of this rank's output shard, in ascending
+    // row order (the order in which the tiles complete on all ranks), dealt
+    // round-robin to the CTAs.  A unit waits for the tile's flag from every rank,
+    // then sums the ranks' partials in ascending rank order in fp32, adds the
+    // bias and writes the output.  Two 16-byte vectors per thread and up to
+    // eight sources are in flight at a time.
+    const int rt = tid - 256;
+    const int row_begin = p.rank * p.rpo;
+    const int row_end = row_begin + p.rpo;
+    const int n_rg = (p.rpo + RS_ROW_GROUP - 1) / RS_ROW_GROUP;
+    const int halves = BN / RS_UNIT_COLS;
+    const int n_units = n_rg * p.NB * halves;
+    uint64_t waited_ns = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+      const int half = u % halves;
+      const int t = u / halves;
+      const int nb = t % p.NB;
+      const int g = t / p.NB;
+      const int r0 = row_begin + g * RS_ROW_GROUP;
+      const int r1 = min(r0 + RS_ROW_GROUP, row_end);
+      const int tile_id = (r0 / BM) * p.NB + nb;
+      if (rt < p.world) {
+        const uint64_t w0 = p.timing ? kb::globaltimer_ns() : 0;
+        if (!kb::wait_flag_ge(rs_flag(p, p.rank, rt, tile_id), p.epoch, p.limit_ns, 256)) {
+          kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_RS_FLAG, (uint32_t)rt, p.epoch);
+        }
+        if (p.timing) waited_ns += kb::globaltimer_ns() - w0;
+      }
+      comm_bar_sync();
+      const int c0 = nb * BN + half * RS_UNIT_COLS;
+      constexpr int VPR = RS_UNIT_COLS / 8;  // 16-byte vectors per unit row
+      const int total = (r1 - r0) * VPR;
+      for (int v0 = rt; v0 < total; v0 += 2 * 128) {
+        float accv[2][8];
+        int rowv[2], colv[2];
+        bool live[2];
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          const int v = v0 + b * 128;
+          rowv[b] = r0 + v / VPR;
+          colv[b] = c0 + (v % VPR) * 8;
+          live[b] = v < total && colv[b] < p.N;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) accv[b][e] = 0.f;
+        }
+        if (p.mc_base != nullptr) {
+          uint4 x[2];
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            x[b] = make_uint4(0u, 0u, 0u, 0u);
+            if (live[b]) {
+              const bf16* src = reinterpret_cast<const bf16*>(p.mc_base + p.data_off) + rs_stage_elem(p, rowv[b]) + colv[b];
+              x[b] = kb::multimem_ld_reduce_bf16x8(src);
+            }
+          }
+#pragma unroll
+          for (int b = 0; b < 2; ++b) unpack8(x[b], accv[b]);
+        } else {
+#pragma unroll 1
+          for (int s0 = 0; s0 < p.world; s0 += 8) {
+            uint4 x[2][8];
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+#pragma unroll
+              for (int sj = 0; sj < 8; ++sj) {
+                x[b][sj] = make_uint4(0u, 0u, 0u, 0u);
+                if (live[b] && s0 + sj < p.world) {
+                  const bf16* src = reinterpret_cast<const bf16*>(p.peer_base[s0 + sj] + p.data_off) +
+                                    rs_stage_elem(p, rowv[b]) + colv[b];
+                  x[b][sj] = kb::ld_sys_v4(src);
+                }
+              }
+            }
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+#pragma unroll
+              for (int sj = 0; sj < 8; ++sj) {
+                float f[8];
+                unpack8(x[b][sj], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) accv[b][e] += f[e];
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          if (!live[b]) continue;
+          if (p.bias != nullptr) {
+            float bz[8];
+            unpack8(*reinterpret_cast<const uint4*>(p.bias + colv[b]), bz);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) accv[b][e] += p.bias_scale * bz[e];
+          }
+          *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(rowv[b] - row_begin) * p.N + colv[b]) = pack8(accv[b]);
+        }
+      }
+    }
+    if (p.status != nullptr && p.timing && rt < p.world) atomicMax(&p.status[5], static_cast<uint32_t>(waited_ns / 1000));
+    if (p.status != nullptr && p.timing && rt == 0) {
       atomicMax(&p.status[7], static_cast<uint32_t>((kb::globaltimer_ns() - t_start) / 1000));
     }
   } else if (kAG && warp >= 8) {
@@ -677,10 +662,12 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     // completes at the aggregate rate instead of the slowest SM's.  A claimed
     // slice is read once (eight 16-byte loads per thread in flight) and stored
     // into the gather buffer of every other rank (and of this rank, unless the
-    // GEMM reads its own rows in place).  Groups therefore arrive everywhere in
-    // ascending order, which is the order in which the GEMMs consume them.  When
-    // a CTA finds a group exhausted it fences and counts itself done; the last
-    // one releases the group's flags on every rank and rewinds the claim counter.
+    // GEMM reads its own rows in place): one peer store per rank, or a single
+    // multimem store that the switch replicates.  Groups therefore arrive
+    // everywhere in ascending order, which is the order in which the GEMMs
+    // consume them.  When a CTA finds a group exhausted it fences and counts
+    // itself done; the last one releases the group's flags on every rank and
+    // rewinds both counters for the next call.
     const int n_chunks = p.own_hi_mb - p.own_lo_mb + 1;
     const int own_row0 = p.rank * p.rpo;
     const int dd0 = p.ag_own_direct ? 1 : 0;
@@ -701,6 +688,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       const size_t nvec = static_cast<size_t>(r_end - r_begin) * p.K / 8;
       const uint32_t n_slices = static_cast<uint32_t>((nvec + SLICE - 1) / SLICE);
       const uint4* src = reinterpret_cast<const uint4*>(p.a_local + static_cast<size_t>(r_begin - own_row0) * p.K);
+      const size_t dst_elem = ag_gather_elem(p, r_begin);
       for (;;) {
         if (ct == 0) s_claim = atomicAdd(&counters[64 + g], 1u);
         comm_bar_sync();
@@ -714,20 +702,30 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           const size_t v = base + u * 128 + ct;
           if (v < nvec) x[u] = kb::ld_nc_v4(src + v);
         }
-        for (int dd = dd0; dd < p.world; ++dd) {
-          const int dst = (p.rank - dd + p.world) % p.world;
-          uint4* dstp = reinterpret_cast<uint4*>(ag_gather_row(p, dst, r_begin));
+        if (p.mc_base != nullptr) {
+          uint4* dstp = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.mc_base + p.data_off) + dst_elem);
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             const size_t v = base + u * 128 + ct;
-            if (v < nvec) kb::st_sys_v4(dstp + v, x[u]);
+            if (v < nvec) kb::multimem_st_v4(dstp + v, x[u]);
+          }
+        } else {
+          for (int dd = dd0; dd < p.world; ++dd) {
+            const int dst = (p.rank - dd + p.world) % p.world;
+            uint4* dstp = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.peer_base[dst] + p.data_off) + dst_elem);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const size_t v = base + u * 128 + ct;
+              if (v < nvec) kb::st_sys_v4(dstp + v, x[u]);
+            }
           }
         }
       }
       if (ct == 0) {
         kb::fence_sys();
         const uint32_t old = atomicAdd(&counters[g], 1u);
-        if ((old + 1u) % gridDim.x == 0u) {
+        if (old == gridDim.x - 1u) {
+          counters[g] = 0u;       // every CTA has counted itself: both counters start the next call at zero
           counters[64 + g] = 0u;  // every CTA is past its last claim of this group
           kb::fence_sys();
           for (int cc = c_lo; cc < c_hi; ++cc) {
@@ -739,7 +737,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
         }
       }
     }
-    if (ct == 0 && p.status != nullptr && (p.debug & 8)) {
+    if (ct == 0 && p.status != nullptr && p.timing) {
       atomicMax(&p.status[6], static_cast<uint32_t>((kb::globaltimer_ns() - t_start) / 1000));
     }
   }
@@ -755,12 +753,12 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
 }
 
 // ------------------------------------------------------------------ host ----
-int make_tmap(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+int make_tmap(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
   auto encode = KB_DRV(cuTensorMapEncodeTiled);
   if (encode == nullptr) return KB_ERR_UNSUPPORTED;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {BK, box_rows};
+  cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -775,9 +773,47 @@ int make_tmap(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, u
 
 inline uint64_t round_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 
-inline bool getenv_flag(const char* name) {
-  const char* v = getenv(name);
-  return v != nullptr && v[0] == '1';
+// Environment switches, read once per process.
+struct EnvConfig {
+  bool no_pair;
+  bool timing;
+  int group_rows;
+  EnvConfig() {
+    const char* v = getenv("KB200_GEMM_NO_PAIR");
+    no_pair = v != nullptr && v[0] == '1';
+    v = getenv("KB200_GEMM_TIMING");
+    timing = v != nullptr && v[0] == '1';
+    v = getenv("KB200_GEMM_GROUP_ROWS");
+    group_rows = (v != nullptr && atoi(v) >= 256) ? atoi(v) : 1024;
+  }
+};
+const EnvConfig& env_config() {
+  static const EnvConfig cfg;
+  return cfg;
+}
+
+// Fills the fields of the tile schedule.  Returns false when CTA pairs were
+// asked for but the rows per rank are not a multiple of 256.
+bool fill_schedule(GemmParams& p, int mode, int M, int N, int rank, int world, bool pair) {
+  p.mode = world > 1 ? mode : KB_GEMM_PLAIN;
+  p.M = M;
+  p.N = N;
+  p.world = world;
+  p.rank = rank;
+  p.MB = (M + BM - 1) / BM;
+  p.NB = (N + BN - 1) / BN;
+  const bool dist_mode = p.mode != KB_GEMM_PLAIN;
+  p.rpo = dist_mode ? M / world : M;
+  if (pair && dist_mode && (p.rpo % 256) != 0) return false;
+  const int block_rows = pair ? 256 : 128;
+  p.MBQ = (M + block_rows - 1) / block_rows;
+  p.own_lo_q = dist_mode ? (rank * p.rpo) / block_rows : 0;
+  p.ag_n_own = (p.mode == KB_GEMM_AG && (p.rpo % block_rows) == 0) ? p.rpo / block_rows : 0;
+  p.rs_nq = (p.mode == KB_GEMM_RS && (p.rpo % block_rows) == 0) ? p.rpo / block_rows : 0;
+  // 1024 rows are swept together (measured best among 512 to 4096 on 8192 x 8192 x 29568; for the all-gather
+  // kernel it also makes the first group consist of this rank's own rows only at eight ranks).
+  p.group = env_config().group_rows / block_rows;
+  return true;
 }
 
 }  // namespace
@@ -789,35 +825,15 @@ extern "C" int kb_gemm_schedule(int mode, int M, int N, int rank, int world, int
   if (M <= 0 || N <= 0 || world < 1 || rank < 0 || rank >= world || (mode != KB_GEMM_PLAIN && M % world != 0)) return -1;
   GemmParams p;
   memset(&p, 0, sizeof(p));
-  p.mode = world > 1 ? mode : KB_GEMM_PLAIN;
-  p.M = M;
-  p.N = N;
-  p.world = world;
-  p.rank = rank;
-  p.MB = (M + BM - 1) / BM;
-  p.NB = (N + BN - 1) / BN;
-  p.rpo = (p.mode == KB_GEMM_PLAIN) ? M : M / world;
-  const int block_rows = pair ? 256 : 128;
-  const bool dist_mode = p.mode != KB_GEMM_PLAIN;
-  if (pair && dist_mode && (p.rpo % 256) != 0) return -1;
-  p.MBQ = (M + block_rows - 1) / block_rows;
-  p.own_lo_q = dist_mode ? (rank * p.rpo) / block_rows : 0;
-  p.own_hi_q = dist_mode ? ((rank + 1) * p.rpo - 1) / block_rows : p.MBQ - 1;
-  p.ag_n_own = (p.mode == KB_GEMM_AG && (p.rpo % block_rows) == 0) ? p.rpo / block_rows : 0;
-  // 1024 rows are swept together (measured best among 512 to 4096 on 8192 x 8192 x 29568; for the all-gather
-  // kernel it also makes the first group consist of this rank's own rows only at eight ranks).
-  p.group = 1024 / block_rows;
-  if (const char* g = getenv("KB200_GEMM_GROUP")) p.group = atoi(g) > 0 ? atoi(g) : p.group;
+  if (!fill_schedule(p, mode, M, N, rank, world, pair != 0)) return -1;
   const int total = p.MBQ * p.NB;
-  if (pos >= 0 && pos < total && block != nullptr && nb != nullptr) {
-    if (pair) tile_at<true>(p, pos, *block, *nb);
-    else tile_at<false>(p, pos, *block, *nb);
-  }
+  if (pos >= 0 && pos < total && block != nullptr && nb != nullptr) tile_at(p, pos, *block, *nb);
   return total;
 }
 
 extern "C" uint64_t kb_gemm_rs_data_bytes(int M, int N, int world) {
-  return round_up(2ull * world * (uint64_t)(M / world) * N * 2, 256);
+  (void)world;
+  return round_up(2ull * (uint64_t)M * N * 2, 256);  // two parities of this rank's [M, N] bf16 partial product
 }
 extern "C" uint64_t kb_gemm_rs_flag_bytes(int M, int N, int world) {
   const uint64_t tiles = (uint64_t)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
@@ -844,67 +860,82 @@ extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {
     kb::set_error("kb_gemm: bad rank/world %d/%d", a->rank, a->world);
     return KB_ERR_ARG;
   }
+  if (a->mode != KB_GEMM_PLAIN && a->mode != KB_GEMM_RS && a->mode != KB_GEMM_AG) {
+    kb::set_error("kb_gemm: unknown mode %d", a->mode);
+    return KB_ERR_ARG;
+  }
   auto misaligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
   if (misaligned(a->A) || misaligned(a->B) || misaligned(a->out) || (a->bias && misaligned(a->bias))) {
     kb::set_error("kb_gemm: operand pointers must be 16-byte aligned");
     return KB_ERR_ARG;
   }
+  const bool dist = a->mode != KB_GEMM_PLAIN && a->world > 1;
+  int rpo = a->M;
+  if (dist) {
+    if (a->M % a->world != 0) {
+      kb::set_error("kb_gemm: M=%d must be divisible by world=%d", a->M, a->world);
+      return KB_ERR_ARG;
+    }
+    rpo = a->M / a->world;
+    if (!((rpo % BM) == 0 || (BM % rpo) == 0)) {
+      kb::set_error("kb_gemm: rows per rank (%d) must divide or be a multiple of %d", rpo, BM);
+      return KB_ERR_ARG;
+    }
+    for (int r = 0; r < a->world; ++r) {
+      if (a->peer_base[r] == nullptr) {
+        kb::set_error("kb_gemm: peer_base[%d] is null", r);
+        return KB_ERR_ARG;
+      }
+    }
+  }
+
+  // CTA pairs need 256-row scheduling blocks that do not straddle two ranks.
+  // num_ctas bit 30 forces the single-CTA kernel (tests, comparisons).
+  const EnvConfig& env = env_config();
+  const bool forbid_pair = (a->num_ctas & (1 << 30)) != 0 || env.no_pair;
+  const int req_ctas = a->num_ctas & ~(1 << 30);
+  bool pair = !forbid_pair && a->M >= 256 && (!dist || (rpo % 256) == 0);
+  int dev = 0, sms = 0;
+  KB_CUDA_OK(cudaGetDevice(&dev));
+  {
+    static int cached_sms[64] = {0};
+    if (dev >= 0 && dev < 64 && cached_sms[dev] > 0) {
+      sms = cached_sms[dev];
+    } else {
+      KB_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      if (dev >= 0 && dev < 64) cached_sms[dev] = sms;
+    }
+  }
+  int grid = req_ctas > 0 ? req_ctas : sms;
+  if (grid > sms) grid = sms;
+  if (pair) {
+    grid &= ~1;
+    if (grid < 2) pair = false;
+  }
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
-  p.mode = a->mode;
-  p.M = a->M;
-  p.N = a->N;
+  fill_schedule(p, a->mode, a->M, a->N, dist ? a->rank : 0, dist ? a->world : 1, pair);
   p.K = a->K;
-  p.MB = (a->M + BM - 1) / BM;
-  p.NB = (a->N + BN - 1) / BN;
   p.KB = (a->K + BK - 1) / BK;
   p.bias = static_cast<const bf16*>(a->bias);
   p.bias_scale = a->bias_scale;
   p.out = static_cast<bf16*>(a->out);
-  p.rank = a->rank;
-  p.world = a->world;
   p.epoch = a->epoch;
   p.status = a->status;
   p.limit_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
   p.data_off = a->data_off;
   p.flag_off = a->flag_off;
   p.counter_off = a->counter_off;
-  p.ag_parts = 32;
-  for (int r = 0; r < a->world; ++r) p.peer_base[r] = static_cast<char*>(a->peer_base[r]);
-
-  const void* a_ptr = a->A;
-  uint64_t a_rows = a->M;
-  p.rpo = a->M;
+  p.timing = env.timing ? 1 : 0;
   p.own_lo_mb = 0;
   p.own_hi_mb = p.MB - 1;
-  const bool dist = a->mode != KB_GEMM_PLAIN && a->world > 1;
-  if (a->mode == KB_GEMM_PLAIN || !dist) {
-    if (a->mode == KB_GEMM_AG) {
-      // Single rank: nothing to gather, read A in place.
-      p.mode = KB_GEMM_PLAIN;
-    }
-    if (a->mode == KB_GEMM_RS) p.mode = KB_GEMM_PLAIN;
-    p.world = 1;
-    p.rank = 0;
-  } else {
-    if (a->M % a->world != 0) {
-      kb::set_error("kb_gemm: M=%d must be divisible by world=%d", a->M, a->world);
-      return KB_ERR_ARG;
-    }
-    p.rpo = a->M / a->world;
-    if (!((p.rpo % BM) == 0 || (BM % p.rpo) == 0)) {
-      kb::set_error("kb_gemm: rows per rank (%d) must divide or be a multiple of %d", p.rpo, BM);
-      return KB_ERR_ARG;
-    }
-    for (int r = 0; r < a->world; ++r) {
-      if (p.peer_base[r] == nullptr) {
-        kb::set_error("kb_gemm: peer_base[%d] is null", r);
-        return KB_ERR_ARG;
-      }
-    }
-    p.own_lo_mb = (a->rank * p.rpo) / BM;
-    p.own_hi_mb = ((a->rank + 1) * p.rpo - 1) / BM;
+  const void* a_ptr = a->A;
+  if (dist) {
+    for (int r = 0; r < a->world; ++r) p.peer_base[r] = static_cast<char*>(a->peer_base[r]);
+    p.mc_base = static_cast<char*>(a->mc_base);
+    p.own_lo_mb = (a->rank * rpo) / BM;
+    p.own_hi_mb = ((a->rank + 1) * rpo - 1) / BM;
     if (a->mode == KB_GEMM_AG) {
       p.a_local = static_cast<const bf16*>(a->A);
       const uint32_t parity = a->epoch & 1u;
@@ -912,62 +943,37 @@ extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {
     }
   }
 
-  // CTA pairs need 256-row scheduling blocks that do not straddle two ranks.
-  // num_ctas bit 30 forces the single-CTA kernel (tests, comparisons).
-  {
-    const char* dbg = getenv("KB200_GEMM_DEBUG");
-    p.debug = dbg ? atoi(dbg) : 0;
-
-  }
-  const bool forbid_pair = (a->num_ctas & (1 << 30)) != 0 || getenv_flag("KB200_GEMM_NO_PAIR");
-  const int req_ctas = a->num_ctas & ~(1 << 30);
-  const bool dist_mode = (p.mode != KB_GEMM_PLAIN);
-  bool pair = !forbid_pair && a->M >= 256 && (!dist_mode || (p.rpo % 256) == 0);
-
-  int dev = 0, sms = 0;
-  KB_CUDA_OK(cudaGetDevice(&dev));
-  KB_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  int grid = req_ctas > 0 ? req_ctas : sms;
-  if (grid > sms) grid = sms;
-  if (pair) {
-    grid &= ~1;
-    if (grid < 2) pair = false;
-  }
-  const int block_rows = pair ? 256 : 128;
-  p.MBQ = (a->M + block_rows - 1) / block_rows;
-  p.own_lo_q = dist_mode ? (a->rank * p.rpo) / block_rows : 0;
-  p.own_hi_q = dist_mode ? ((a->rank + 1) * p.rpo - 1) / block_rows : p.MBQ - 1;
-  p.ag_n_own = (p.mode == KB_GEMM_AG && (p.rpo % block_rows) == 0) ? p.rpo / block_rows : 0;
-  // 1024 rows are swept together (measured best among 512 to 4096 on 8192 x 8192 x 29568; for the all-gather
-  // kernel it also makes the first group consist of this rank's own rows only at eight ranks).
-  p.group = 1024 / block_rows;
-  if (const char* g = getenv("KB200_GEMM_GROUP")) p.group = atoi(g) > 0 ? atoi(g) : p.group;
-
-  int rc = make_tmap(&p.tmA, a_ptr, a_rows, a->K, BM);
+  int rc = make_tmap(&p.tmA, a_ptr, a->M, a->K, BK, BM);
   if (rc != KB_OK) return rc;
-  rc = make_tmap(&p.tmB, a->B, a->N, a->K, pair ? 128 : BN);
+  rc = make_tmap(&p.tmB, a->B, a->N, a->K, BK, pair ? 128 : BN);
   if (rc != KB_OK) return rc;
-  p.ag_own_direct = 0;
-  if (p.mode == KB_GEMM_AG && (p.rpo % BM) == 0) {
-    rc = make_tmap(&p.tmOwn, a->A, p.rpo, a->K, BM);
+  if (p.mode == KB_GEMM_AG && (rpo % BM) == 0) {
+    rc = make_tmap(&p.tmOwn, a->A, rpo, a->K, BK, BM);
     if (rc != KB_OK) return rc;
     p.ag_own_direct = 1;
   }
+  if (p.mode != KB_GEMM_RS) {
+    rc = make_tmap(&p.tmOut, a->out, a->M, a->N, OUT_BOX_COLS, OUT_BOX_ROWS);
+    if (rc != KB_OK) return rc;
+  }
 
   const int total_units = p.MBQ * p.NB * (pair ? 2 : 1);
-  const bool ag = (p.mode == KB_GEMM_AG);
-  if (!ag && grid > total_units) grid = total_units;
+  if (p.mode == KB_GEMM_PLAIN && grid > total_units) grid = total_units;  // the fused modes keep every CTA: their extra warps share the transfers
 
-  const int threads = ag ? THREADS_AG : THREADS_BASE;
-  const void* fn = nullptr;
-  if (pair) {
-    fn = ag ? (const void*)gemm_kernel<KB_GEMM_AG, true>
-            : (p.mode == KB_GEMM_RS ? (const void*)gemm_kernel<KB_GEMM_RS, true> : (const void*)gemm_kernel<KB_GEMM_PLAIN, true>);
-  } else {
-    fn = ag ? (const void*)gemm_kernel<KB_GEMM_AG, false>
-            : (p.mode == KB_GEMM_RS ? (const void*)gemm_kernel<KB_GEMM_RS, false> : (const void*)gemm_kernel<KB_GEMM_PLAIN, false>);
+  const int threads = p.mode == KB_GEMM_PLAIN ? THREADS_BASE : THREADS_COMM;
+  const void* fns[2][3] = {
+      {(const void*)gemm_kernel<KB_GEMM_PLAIN, false>, (const void*)gemm_kernel<KB_GEMM_RS, false>,
+       (const void*)gemm_kernel<KB_GEMM_AG, false>},
+      {(const void*)gemm_kernel<KB_GEMM_PLAIN, true>, (const void*)gemm_kernel<KB_GEMM_RS, true>,
+       (const void*)gemm_kernel<KB_GEMM_AG, true>}};
+  const void* fn = fns[pair ? 1 : 0][p.mode];
+  {
+    static bool attr_set[64][2][3] = {};
+    if (dev < 0 || dev >= 64 || !attr_set[dev][pair ? 1 : 0][p.mode]) {
+      KB_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      if (dev >= 0 && dev < 64) attr_set[dev][pair ? 1 : 0][p.mode] = true;
+    }
   }
-  KB_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(threads);

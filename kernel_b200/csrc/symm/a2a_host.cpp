@@ -66,7 +66,8 @@ struct Layout {
     return reinterpret_cast<int32_t*>(base[on] + count_off) + static_cast<size_t>(src) * El;
   }
   std::atomic<uint32_t>* flag(int on, int which, int src) const {
-    return reinterpret_cast<std::atomic<uint32_t>*>(base[on] + flag_off) + which * world + src;
+    // same layout as the kernels: one 128-byte line per (phase, source)
+    return reinterpret_cast<std::atomic<uint32_t>*>(base[on] + flag_off) + static_cast<size_t>(which * KB_MAX_WORLD + src) * 32;
   }
 };
 

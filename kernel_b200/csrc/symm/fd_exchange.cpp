@@ -114,6 +114,17 @@ bool recv_msg(int sock, Header* h, int* fd, int64_t deadline) {
   return true;
 }
 
+// The other end of a connected Unix socket must run under this process's user:
+// abstract socket names are visible to every process of the network namespace, so
+// a foreign process could bind a rank's name first (and be sent a memory handle)
+// or connect and hand in a descriptor of its own.
+bool peer_is_same_user(int sock) {
+  ucred cred;
+  socklen_t len = sizeof(cred);
+  if (getsockopt(sock, SOL_SOCKET, SO_PEERCRED, &cred, &len) != 0 || len != sizeof(cred)) return false;
+  return cred.uid == geteuid();
+}
+
 }  // namespace
 
 extern "C" int kb_fd_allgather(const char* session, const char* tag, int rank, int world, int my_fd, int* out_fds,
@@ -160,6 +171,10 @@ extern "C" int kb_fd_allgather(const char* session, const char* tag, int rank, i
       if (pr <= 0) continue;
       const int c = accept4(lsock, nullptr, nullptr, SOCK_CLOEXEC);
       if (c < 0) continue;
+      if (!peer_is_same_user(c)) {
+        close(c);
+        continue;  // not one of this job's ranks
+      }
       Header h;
       int fd = -1;
       const bool ok = recv_msg(c, &h, &fd, deadline);
@@ -195,6 +210,11 @@ extern "C" int kb_fd_allgather(const char* session, const char* tag, int rank, i
         break;
       }
       if (connect(c, reinterpret_cast<sockaddr*>(&paddr), plen) == 0) {
+        if (!peer_is_same_user(c)) {
+          close(c);
+          send_status = KB_ERR_IO;  // somebody else owns the peer's name: hand nothing over
+          break;
+        }
         Header h = {kMagic, rank, my_fd >= 0 ? 1 : 0};
         const bool ok = send_msg(c, h, my_fd);
         close(c);

@@ -2,11 +2,12 @@
 // host-backed symmetric heap (KB_BACKEND_HOST).  It is the protocol of
 // kernels/gemm_sm100.cu with one worker per rank: the same 128 x 256 tiles
 // visited in the order of the kernel's static schedule (kb_gemm_schedule), the
-// same staging layouts ([parity][source][row][N] bf16 partial tiles for the
-// reduce-scatter, [parity][row][K] gathered rows for the all-gather), the same
-// per-(source, tile) and per-(source, row block) epoch flags with
-// release/acquire ordering, fp32 accumulation, the owner's own partial kept in
-// fp32 and the other ranks' bf16 partials added in ascending rank order.
+// same staging layouts (this rank's [parity][M][N] bf16 partial product for the
+// reduce-scatter, which the row owners pull; [parity][row][K] gathered rows for
+// the all-gather), the same per-(source, tile) and per-(source, row block) epoch
+// flags with release/acquire ordering, fp32 accumulation, and the ranks' bf16
+// partials added in fp32 in ascending rank order before the bias and the one
+// rounding of the result.
 // std::atomic stands in for system-scope PTX and memcpy for peer stores.
 //
 // Purpose: the index arithmetic, the epoch/parity protocol and the time-outs
@@ -62,9 +63,10 @@ struct Ctx {
     return reinterpret_cast<std::atomic<uint32_t>*>(base(on) + a->flag_off) +
            (static_cast<size_t>(parity) * a->world + src) * (static_cast<size_t>(MB) * NB) + tile;
   }
-  uint16_t* rs_row(int on, int src, int row_local) const {
+  // row `row` of rank `on`'s partial product of this epoch
+  uint16_t* rs_row(int on, int row) const {
     return reinterpret_cast<uint16_t*>(base(on) + a->data_off) +
-           ((static_cast<size_t>(parity) * a->world + src) * rpo + row_local) * static_cast<size_t>(a->N);
+           (static_cast<size_t>(parity) * a->M + row) * static_cast<size_t>(a->N);
   }
   // all-gather
   std::atomic<uint32_t>* ag_flag(int on, int src, int mb) const {
@@ -121,6 +123,9 @@ int run_rs(const Ctx& c) {
     kb::set_error("gemm host: bad problem for the schedule");
     return KB_ERR_ARG;
   }
+  // GEMM part: every tile of this rank's partial product goes, as bf16, into its
+  // own staging matrix; the owners of the tile's rows are told.  Nothing here
+  // waits for a peer.
   std::vector<float> acc(static_cast<size_t>(BM) * BN), bt;
   for (int pos = 0; pos < total; ++pos) {
     int mb = 0, nb = 0;
@@ -129,39 +134,46 @@ int run_rs(const Ctx& c) {
     const int c0 = nb * BN, cols = (a->N - c0 < BN) ? a->N - c0 : BN;
     const int tile = mb * c.NB + nb;
     tile_matmul([&](int i) { return A + static_cast<size_t>(r0 + i) * a->K; }, rows, B, c0, cols, a->K, bt, acc.data());
-    const int o_lo = r0 / c.rpo, o_hi = (r0 + rows - 1) / c.rpo;
-    // partial rows of other owners: bf16 into their staging, then the flag
     for (int i = 0; i < rows; ++i) {
-      const int owner = (r0 + i) / c.rpo;
-      if (owner == a->rank) continue;
-      uint16_t* dst = c.rs_row(owner, a->rank, r0 + i - owner * c.rpo) + c0;
+      uint16_t* dst = c.rs_row(a->rank, r0 + i) + c0;
       const float* src = acc.data() + static_cast<size_t>(i) * cols;
       for (int j = 0; j < cols; ++j) dst[j] = f32_to_bf16(src[j]);
     }
-    for (int o = o_lo; o <= o_hi; ++o) {
-      if (o != a->rank) c.rs_flag(o, a->rank, tile)->store(a->epoch, std::memory_order_release);
+    for (int o = r0 / c.rpo; o <= (r0 + rows - 1) / c.rpo; ++o) {
+      c.rs_flag(o, a->rank, tile)->store(a->epoch, std::memory_order_release);
     }
-    if (a->rank < o_lo || a->rank > o_hi) continue;
-    // own rows: own partial in fp32 + the other ranks' bf16 partials in rank order + bias
-    for (int s = 0; s < a->world; ++s) {
-      if (s == a->rank) continue;
-      const int rc = wait_flag(c, c.rs_flag(a->rank, s, tile), s, "partial tile");
-      if (rc != KB_OK) return rc;
-    }
-    for (int i = 0; i < rows; ++i) {
-      const int gr = r0 + i;
-      if (gr / c.rpo != a->rank) continue;
-      const int rl = gr - a->rank * c.rpo;
-      float* row = acc.data() + static_cast<size_t>(i) * cols;
+  }
+  // Reduction part: the rows this rank owns, in units of 64 rows x 128 columns in
+  // ascending row order; a unit waits for its tile's flag from every rank and
+  // pulls the partials.
+  constexpr int RG = 64, UC = 128;
+  const int row_begin = a->rank * c.rpo, row_end = row_begin + c.rpo;
+  const int n_rg = (c.rpo + RG - 1) / RG;
+  std::vector<float> sum(UC);
+  for (int g = 0; g < n_rg; ++g) {
+    const int r0 = row_begin + g * RG, r1 = (r0 + RG < row_end) ? r0 + RG : row_end;
+    for (int nb = 0; nb < c.NB; ++nb) {
+      const int tile = (r0 / BM) * c.NB + nb;
       for (int s = 0; s < a->world; ++s) {
-        if (s == a->rank) continue;
-        const uint16_t* st = c.rs_row(a->rank, s, rl) + c0;
-        for (int j = 0; j < cols; ++j) row[j] += bf16_to_f32(st[j]);
+        const int rc = wait_flag(c, c.rs_flag(a->rank, s, tile), s, "partial tile");
+        if (rc != KB_OK) return rc;
       }
-      uint16_t* o = out + static_cast<size_t>(rl) * a->N + c0;
-      for (int j = 0; j < cols; ++j) {
-        const float b = bias != nullptr ? a->bias_scale * bf16_to_f32(bias[c0 + j]) : 0.f;
-        o[j] = f32_to_bf16(row[j] + b);
+      for (int half = 0; half < BN / UC; ++half) {
+        const int c0 = nb * BN + half * UC;
+        const int cols = (a->N - c0 < UC) ? a->N - c0 : UC;
+        if (cols <= 0) continue;
+        for (int row = r0; row < r1; ++row) {
+          for (int j = 0; j < cols; ++j) sum[j] = 0.f;
+          for (int s = 0; s < a->world; ++s) {
+            const uint16_t* st = c.rs_row(s, row) + c0;
+            for (int j = 0; j < cols; ++j) sum[j] += bf16_to_f32(st[j]);
+          }
+          uint16_t* o = out + static_cast<size_t>(row - row_begin) * a->N + c0;
+          for (int j = 0; j < cols; ++j) {
+            const float b = bias != nullptr ? a->bias_scale * bf16_to_f32(bias[c0 + j]) : 0.f;
+            o[j] = f32_to_bf16(sum[j] + b);
+          }
+        }
       }
     }
   }

@@ -275,7 +275,9 @@ extern "C" int kb_symm_mc_create(KbSymmHeap* h, int* fd_out) {
   if (!getGran || !create || !exportH) return KB_ERR_UNSUPPORTED;
   CUmulticastObjectProp prop = mc_prop(h, h->seg_bytes);
   size_t gran = 0;
-  KB_CU_OK(getGran(&gran, &prop, CU_MULTICAST_GRANULARITY_RECOMMENDED), "cuMulticastGetGranularity");
+  // The minimum granularity (the recommended one can be hundreds of megabytes); segments are whole
+  // multiples of the 2 MB allocation granularity, which the minimum divides on NVSwitch systems.
+  KB_CU_OK(getGran(&gran, &prop, CU_MULTICAST_GRANULARITY_MINIMUM), "cuMulticastGetGranularity");
   h->mc_bytes = round_up(h->seg_bytes, gran);
   if (h->mc_bytes != h->seg_bytes) {
     kb::set_error("multicast granularity %zu does not divide the segment size %llu", gran,

@@ -50,7 +50,8 @@ from .stats import Stats, calculate_stats, should_stop
 from .testcases import SpecError, TestCase, cases_from_yaml, parse_tests
 
 EXIT_OK, EXIT_USAGE, EXIT_NO_FD, EXIT_FAIL, EXIT_BAD_TESTS = 0, 2, 111, 112, 113
-TEST_TIMEOUT_S, BENCH_TIMEOUT_S = 120, 240
+TEST_TIMEOUT_S = float(os.environ.get("KB200_EVAL_TEST_TIMEOUT_S", "120"))
+BENCH_TIMEOUT_S = float(os.environ.get("KB200_EVAL_BENCH_TIMEOUT_S", "240"))
 
 
 class PopcornOutput:
@@ -141,7 +142,14 @@ def clone_data(data, device: torch.device):
     if isinstance(data, torch.Tensor):
         return data.detach().clone().to(device)
     if isinstance(data, tuple):
-        return tuple(clone_data(x, device) for x in data)
+        items = tuple(clone_data(x, device) for x in data)
+        if type(data) is tuple:
+            return items
+        if hasattr(data, "rebuilt"):  # a task's tuple type that carries case attributes
+            return data.rebuilt(items)
+        if hasattr(data, "_fields"):  # namedtuple
+            return type(data)(*items)
+        return items
     if isinstance(data, list):
         return [clone_data(x, device) for x in data]
     if isinstance(data, dict):
@@ -373,11 +381,52 @@ def run_profile(cfg: RunConfig, test: TestCase, rank: int) -> str:
 
 
 # --------------------------------------------------------------- pool front ----
+class WorkerPool:
+    """The spawn pool of the per-rank workers, replaceable after a time-out.
+
+    A case that ran into its time limit leaves its workers running: they hold the
+    rendezvous, their GPUs and possibly a device-side wait, and the next case would
+    be queued behind them (the reference's evaluator has the same weakness,
+    ``eval.py:201``).  ``rebuild`` terminates those processes and starts fresh ones."""
+
+    def __init__(self, n_workers: int):
+        self.n_workers = n_workers
+        self._ctx = multiprocessing.get_context("spawn")
+        self.pool = self._ctx.Pool(n_workers)
+        self.rebuilds = 0
+
+    def rebuild(self) -> None:
+        self.pool.terminate()
+        self.pool.join()
+        self.pool = self._ctx.Pool(self.n_workers)
+        self.rebuilds += 1
+
+    def apply(self, fn, args):
+        return self.pool.apply(fn, args)
+
+    def apply_async(self, fn, args):
+        return self.pool.apply_async(fn, args)
+
+    def close(self) -> None:
+        self.pool.terminate()
+        self.pool.join()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
 class Runner:
-    """Dispatches the per-rank workers of every case onto a spawn pool."""
+    """Dispatches the per-rank workers of every case onto the worker pool."""
 
     def __init__(self, pool, n_gpus: int, task: Optional[str], impl: str, backend: str):
         self.pool, self.n_gpus, self.task, self.impl, self.backend = pool, n_gpus, task, impl, backend
+
+    def _timed_out(self) -> None:
+        if hasattr(self.pool, "rebuild"):
+            self.pool.rebuild()
 
     def _cfg(self, test: TestCase) -> RunConfig:
         return RunConfig(task=self.task or guess_task(test.args), impl=self.impl, backend=self.backend, port=free_port())
@@ -398,13 +447,17 @@ class Runner:
             return self.pool.apply(run_local_test, (cfg, test))
         pending = [self.pool.apply_async(run_distributed_test, (cfg, test, r)) for r in range(world)]
         results = []
+        timed_out = False
         for r, p in enumerate(pending):
             try:
-                results.append(p.get(TEST_TIMEOUT_S))
+                results.append(p.get(1 if timed_out else TEST_TIMEOUT_S))
             except multiprocessing.TimeoutError:
+                timed_out = True
                 results.append((False, f"timed out after {TEST_TIMEOUT_S} s"))
             except Exception as e:  # worker raised
                 results.append((False, f"{type(e).__name__}: {e}"))
+        if timed_out:
+            self._timed_out()
         ok = all(r[0] for r in results)
         errors = "\n".join(f"rank {i} - {r[1]}" for i, r in enumerate(results) if not r[0])
         return ok, errors
@@ -420,13 +473,17 @@ class Runner:
         pending = [self.pool.apply_async(run_distributed_benchmark, (cfg, test, r, recheck, max_repeats, max_time_ns))
                    for r in range(world)]
         results = []
+        timed_out = False
         for p in pending:
             try:
-                results.append(p.get(BENCH_TIMEOUT_S))
+                results.append(p.get(1 if timed_out else BENCH_TIMEOUT_S))
             except multiprocessing.TimeoutError:
+                timed_out = True
                 results.append(f"timed out after {BENCH_TIMEOUT_S} s")
             except Exception as e:
                 results.append(f"{type(e).__name__}: {e}")
+        if timed_out:
+            self._timed_out()
         failed = [(i, r) for i, r in enumerate(results) if not isinstance(r, Stats)]
         if failed:
             return "\n".join(f"rank {i} - {msg}" for i, msg in failed)
@@ -588,8 +645,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                 t.args["world_size"] = ns.world
 
     with PopcornOutput(int(fd)) as logger:
-        ctx = multiprocessing.get_context("spawn")
-        with ctx.Pool(n_gpus) as pool:
+        with WorkerPool(n_gpus) as pool:
             runner = Runner(pool, n_gpus, ns.task, ns.submission or ns.impl, ns.backend)
             if ns.mode == "test":
                 return run_testing(logger, runner, tests)

@@ -71,14 +71,16 @@ class MoEAllToAll:
             eb = torch.empty((), dtype=dtype).element_size()
             rows = int(lib.kb_a2a_rows_bytes(self.world, max_num_tokens, experts_per_token, hidden_dim, eb))
             counts = (self.world * self.El * 4 + 255) // 256 * 256
-            need = 2 * rows + counts + 256 + 256 + 4096
+            flag_bytes, sync_bytes = int(lib.kb_a2a_flag_bytes()), int(lib.kb_a2a_sync_bytes())
+            need = 2 * rows + counts + flag_bytes + sync_bytes + 4096
             self.heap = heap or (SymmHeap(need, group=group, device=device) if self.native
                                  else SymmHeap(need, group=group, backend="host", timeout_s=_WAIT_LIMIT_NS / 1e9 + 5))
             self.recv_off = self.heap.alloc(rows)
             self.y_off = self.heap.alloc(rows)
             self.count_off = self.heap.alloc(counts)
-            self.flag_off = self.heap.alloc(256)
-            self.sync_off = self.heap.alloc(256)
+            self.flag_off = self.heap.alloc(flag_bytes)
+            self.sync_off = self.heap.alloc(sync_bytes)
+            self._flag_stride = int(lib.kb_a2a_flag_stride_words())
             self.slots = torch.empty(self.cap, dtype=torch.int32, device=self.heap.device)
             self.status = self.heap.status
             self._eb = eb
@@ -111,7 +113,7 @@ class MoEAllToAll:
         return a
 
     # -------------------------------------------------------------- tracing ----
-    TRACE_PHASES = ("slots", "push", "dispatch_flag", "wait_dispatch", "counts", "expert_rows", "expert_flag",
+    TRACE_PHASES = ("slots", "push", "dispatch_flag", "wait_first_source", "expert_pass", "expert_flag",
                     "wait_expert", "combine")
 
     def enable_trace(self, on: bool = True) -> None:
@@ -122,10 +124,15 @@ class MoEAllToAll:
 
     def read_trace(self) -> dict:
         """Durations in microseconds between consecutive stamps of the last call
-        (synchronises).  ``total`` is entry to end as seen by CTA 0."""
+        (synchronises).  ``expert_pass`` runs source by source and contains the waits
+        for the later sources; ``waited_in_expert_pass`` is their sum,
+        ``waited_for_combine`` the wait for every rank's expert outputs.  ``total`` is
+        entry to end as seen by CTA 0."""
         t = self._trace.cpu().tolist()
         out = {name: (t[i + 1] - t[i]) / 1e3 for i, name in enumerate(self.TRACE_PHASES)}
-        out["total"] = (t[9] - t[0]) / 1e3
+        out["waited_in_expert_pass"] = t[10] / 1e3
+        out["waited_for_combine"] = t[11] / 1e3
+        out["total"] = (t[8] - t[0]) / 1e3
         return out
 
     def _validate(self, x, indices, weights) -> None:
@@ -209,7 +216,8 @@ class MoEAllToAll:
         st = torch.cuda.current_stream(x.device).cuda_stream
         N.check(lib.kb_a2a_dispatch(C.byref(a), st))
         flags = self.heap.peer_ptr(self.rank) + self.flag_off
-        N.check(lib.kb_wait_flags(flags, self.world, self.epoch, _WAIT_LIMIT_NS, self.status.data_ptr(), st))
+        N.check(lib.kb_wait_flags(flags, self.world, self._flag_stride, self.epoch, _WAIT_LIMIT_NS,
+                                  self.status.data_ptr(), st))
         launch_count += 2
         counts = self.heap.tensor(self.count_off, (self.world, self.El), torch.int32)
         recv = self.heap.tensor(self.recv_off, (self.world, self.cap, self.H), self.dtype)
@@ -233,13 +241,29 @@ class MoEAllToAll:
             return out
         lib = N.lib()
         st = torch.cuda.current_stream(x_like.device).cuda_stream
-        # y-ready flags of this epoch go out through a barrier-style post.
-        pad = self.flag_off + 4 * self.world
-        N.check(lib.kb_device_barrier(self.heap.peer_array(), pad, self.rank, self.world, self.epoch, _WAIT_LIMIT_NS,
-                                      self.status.data_ptr(), st))
+        # y-ready flags of this epoch go out first; the combine kernel waits for every rank's.
+        N.check(lib.kb_a2a_post_ready(C.byref(a), st))
         N.check(lib.kb_a2a_combine(C.byref(a), st))
         launch_count += 2
         return out
+
+    def recover(self) -> None:
+        """Collective.  Brings the context back into a usable state after
+        ``heap.check_status()`` reported a failed wait (a peer that was late or
+        absent): waits for this rank's kernels, clears the status words, zeroes the
+        block counters and arrival words, and moves every rank to the same call
+        number, past every flag value already written."""
+        if self.heap is None:
+            return
+        if self.native:
+            torch.cuda.synchronize(self.heap.device)
+        self.heap.status.zero_()
+        words = int(self._lib.kb_a2a_sync_bytes()) // 4
+        self.heap.tensor(self.sync_off, (words,), torch.int32).zero_()
+        self.epoch = self.heap.agree_epoch(self.epoch) + 1
+        if self.native:
+            torch.cuda.synchronize(self.heap.device)
+        self.heap._control_barrier()
 
     # ------------------------------------------------------- debug checks ----
     _POISON = 0x7FC1  # a bf16/fp16 NaN bit pattern that no kernel produces

@@ -50,8 +50,13 @@ def _cpu_heap_path() -> bool:
 
 def _new_heap(nbytes: int, group, device, native: bool) -> SymmHeap:
     if native:
-        return SymmHeap(nbytes, group=group, device=device)
+        return SymmHeap(nbytes, group=group, device=device)  # with an NVLS multicast mapping when KB200_NVLS=1
     return SymmHeap(nbytes, group=group, backend="host", timeout_s=_WAIT_LIMIT_NS / 1e9 + 5)
+
+
+def _mc_base(heap: Optional[SymmHeap]):
+    """Multicast mapping of the heap for the kernels, or None (peer loads and stores)."""
+    return heap.mc_ptr if heap is not None and getattr(heap, "mc_ptr", None) else None
 
 
 def _host_args(ctx, mode: int, M: int, Nn: int, K: int, a, w, bias, bias_scale: float, out) -> N.GemmArgs:
@@ -109,6 +114,69 @@ def _tuned_pair(args: N.GemmArgs, device: torch.device) -> bool:
     args.num_ctas = base
     _pair_choice[key] = times[True] <= times[False]
     return _pair_choice[key]
+
+
+class _HostPipeline:
+    """Streams, events and device buffers of a ``run_from_host`` call: chunk i+1 is
+    copied in on one stream while chunk i runs on the caller's stream and chunk
+    i-1's result is copied out on a third.  Two input and two output buffers.  For
+    CPU ranks the three steps simply run one after the other."""
+
+    def __init__(self, device: torch.device, in_shape, out_shape):
+        self.cuda = device.type == "cuda"
+        self.device = device
+        if self.cuda:
+            self.h2d, self.d2h = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        self.inp = [torch.empty(in_shape, dtype=torch.bfloat16, device=device) for _ in range(2)]
+        self.out = [torch.empty(out_shape, dtype=torch.bfloat16, device=device) for _ in range(2)]
+
+    def begin(self, chunks: int) -> None:
+        if self.cuda:
+            self.cur = torch.cuda.current_stream(self.device)
+            self.in_ready, self.computed, self.out_done = ([torch.cuda.Event() for _ in range(chunks)] for _ in range(3))
+            self.h2d.wait_stream(self.cur)
+
+    def copy_in(self, i: int, fn) -> None:
+        if not self.cuda:
+            return fn()
+        with torch.cuda.stream(self.h2d):
+            if i >= 2:
+                self.h2d.wait_event(self.computed[i - 2])  # the kernel that read this buffer has finished
+            fn()
+            self.in_ready[i].record(self.h2d)
+
+    def compute(self, i: int, fn) -> None:
+        if not self.cuda:
+            return fn()
+        self.cur.wait_event(self.in_ready[i])
+        if i >= 2:
+            self.cur.wait_event(self.out_done[i - 2])  # its previous result has left the output buffer
+        fn()
+        self.computed[i].record(self.cur)
+
+    def copy_out(self, i: int, fn) -> None:
+        if not self.cuda:
+            return fn()
+        with torch.cuda.stream(self.d2h):
+            self.d2h.wait_event(self.computed[i])
+            fn()
+            self.out_done[i].record(self.d2h)
+
+    def end(self) -> None:
+        if self.cuda:
+            self.cur.wait_stream(self.d2h)
+
+
+def _host_buffer(shape) -> torch.Tensor:
+    t = torch.empty(shape, dtype=torch.bfloat16)
+    return t.pin_memory() if torch.cuda.is_available() else t
+
+
+def _check_pinned(t: torch.Tensor, name: str, shape) -> None:
+    if t.is_cuda or t.dtype != torch.bfloat16 or tuple(t.shape) != tuple(shape) or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous bf16 host tensor of shape {tuple(shape)}")
+    if torch.cuda.is_available() and not t.is_pinned() and not os.environ.get("KB200_ALLOW_PAGEABLE"):
+        raise ValueError(f"{name} must be in pinned host memory (tensor.pin_memory()), or the copies cannot overlap the kernel")
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
@@ -226,6 +294,7 @@ class GemmRS:
             if self.heap is not None:
                 args.peer_base = self.heap.peer_array()
                 args.data_off, args.flag_off = self.data_off, self.flag_off
+                args.mc_base = _mc_base(self.heap)
             args.status = self.status.data_ptr()
             args.wait_limit_ns = _WAIT_LIMIT_NS
         args.K = K
@@ -238,6 +307,75 @@ class GemmRS:
             args.num_ctas = 0 if _tuned_pair(args, a.device) else _NO_PAIR_BIT
         _launch(args, a.device)
         return out
+
+    def recover(self) -> None:
+        """Collective.  After ``heap.check_status()`` reported a failed wait: waits
+        for this rank's kernels, clears the status words and moves every rank to the
+        same call number, past every flag value already written."""
+        if self.heap is None:
+            return
+        if self.native:
+            torch.cuda.synchronize(self.heap.device)
+        self.heap.status.zero_()
+        self.epoch = self.heap.agree_epoch(self.epoch) + 1
+        self.heap._control_barrier()
+
+    def run_from_host(self, a_host: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                      bias_scale: float = 1.0, out_host: Optional[torch.Tensor] = None, chunks: int = 4) -> torch.Tensor:
+        """The op with its activations in pinned host memory and its result wanted
+        there: ``a_host [M, K_local]`` -> ``out_host [M/world, N]`` (``w``, ``bias`` on
+        the device).  The rows every rank owns are cut into ``chunks`` pieces; piece i
+        of all owners forms a problem of ``M/chunks`` rows that runs through the
+        same fused kernel, while piece i+1 is on its way in and the result of
+        piece i-1 on its way out (one ``cudaMemcpyAsync`` per contiguous block), so
+        the PCIe transfers overlap the kernel instead of bracketing it.  Returns
+        ``out_host``; the caller's stream is done when everything has arrived.
+        Collective like ``__call__``.  The reference has no counterpart (its
+        evaluator clones the inputs on the device inside its timed region,
+        ``eval.py:358``)."""
+        world, M, Nn = self.world, self.M, self.N
+        rows_rank = M // world
+        while chunks > 1 and (rows_rank % chunks or _rows_bad(rows_rank // chunks)):
+            chunks -= 1
+        rows = rows_rank // chunks
+        K = a_host.shape[1]
+        _check_pinned(a_host, "a_host", (M, K))
+        if out_host is None:
+            out_host = _host_buffer((rows_rank, Nn))
+        _check_pinned(out_host, "out_host", (rows_rank, Nn))
+        dev = w.device
+        key = (chunks, K)
+        st = self._stream_state.get(key) if hasattr(self, "_stream_state") else None
+        if st is None:
+            if not hasattr(self, "_stream_state"):
+                self._stream_state = {}
+            sub = self if chunks == 1 else GemmRS(M // chunks, Nn, group=self.group, device=dev)
+            st = self._stream_state[key] = (sub, _HostPipeline(dev, (world, rows, K), (rows, Nn)))
+        sub, pipe = st
+        src = a_host.view(world, chunks, rows, K)
+        dst = out_host.view(chunks, rows, Nn)
+        pipe.begin(chunks)
+        for i in range(chunks):
+            buf, res = pipe.inp[i % 2], pipe.out[i % 2]
+
+            def copy_in():
+                for r in range(world):
+                    buf[r].copy_(src[r, i], non_blocking=True)
+
+            pipe.copy_in(i, copy_in)
+            pipe.compute(i, lambda: sub(buf.view(world * rows, K), w, bias, bias_scale=bias_scale, out=res))
+            pipe.copy_out(i, lambda: dst[i].copy_(res, non_blocking=True))
+        pipe.end()
+        return out_host
+
+    def close(self) -> None:
+        """Frees this context's workspaces (collective)."""
+        for sub, _ in getattr(self, "_stream_state", {}).values():
+            if sub is not self and sub.heap is not None:
+                sub.heap.close()
+        self._stream_state = {}
+        if self.heap is not None:
+            self.heap.close()
 
 
 class AGGemm:
@@ -313,6 +451,7 @@ class AGGemm:
             if self.heap is not None:
                 args.peer_base = self.heap.peer_array()
                 args.data_off, args.flag_off, args.counter_off = self.data_off, self.flag_off, self.counter_off
+                args.mc_base = _mc_base(self.heap)
             args.status = self.status.data_ptr()
             args.wait_limit_ns = _WAIT_LIMIT_NS
         args.N = Nl
@@ -324,3 +463,71 @@ class AGGemm:
             args.num_ctas = 0 if _tuned_pair(args, a_local.device) else _NO_PAIR_BIT
         _launch(args, a_local.device)
         return out
+
+    def recover(self) -> None:
+        """Collective.  After ``heap.check_status()`` reported a failed wait: waits
+        for this rank's kernels, clears the status words, zeroes the push counters
+        and moves every rank to the same call number, past every flag value already
+        written."""
+        if self.heap is None:
+            return
+        if self.native:
+            torch.cuda.synchronize(self.heap.device)
+        self.heap.status.zero_()
+        self.heap.tensor(self.counter_off, (256,), torch.int32).zero_()
+        self.epoch = self.heap.agree_epoch(self.epoch) + 1
+        if self.native:
+            torch.cuda.synchronize(self.heap.device)
+        self.heap._control_barrier()
+
+    def run_from_host(self, a_host: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                      out_host: Optional[torch.Tensor] = None, chunks: int = 4) -> torch.Tensor:
+        """The op with its activations in pinned host memory and its result wanted
+        there: ``a_host [M/world, K]`` -> ``out_host [M, N_local]``.  This rank's rows
+        are cut into ``chunks`` pieces; piece i of every rank forms a gathered problem
+        of ``M/chunks`` rows for the same fused kernel, overlapped with the copy of
+        piece i+1 coming in and of piece i-1's result going out (see
+        ``GemmRS.run_from_host``).  Collective like ``__call__``."""
+        world, M, K = self.world, self.M, self.K
+        rows_rank = M // world
+        while chunks > 1 and (rows_rank % chunks or _rows_bad(rows_rank // chunks)):
+            chunks -= 1
+        rows = rows_rank // chunks
+        Nl = w.shape[0]
+        _check_pinned(a_host, "a_host", (rows_rank, K))
+        if out_host is None:
+            out_host = _host_buffer((M, Nl))
+        _check_pinned(out_host, "out_host", (M, Nl))
+        dev = w.device
+        key = (chunks, Nl)
+        st = self._stream_state.get(key) if hasattr(self, "_stream_state") else None
+        if st is None:
+            if not hasattr(self, "_stream_state"):
+                self._stream_state = {}
+            sub = self if chunks == 1 else AGGemm(M // chunks, K, group=self.group, device=dev)
+            st = self._stream_state[key] = (sub, _HostPipeline(dev, (rows, K), (world, rows, Nl)))
+        sub, pipe = st
+        src = a_host.view(chunks, rows, K)
+        dst = out_host.view(world, chunks, rows, Nl)
+        pipe.begin(chunks)
+        for i in range(chunks):
+            buf, res = pipe.inp[i % 2], pipe.out[i % 2]
+
+            def copy_out():
+                for r in range(world):
+                    dst[r, i].copy_(res[r], non_blocking=True)
+
+            pipe.copy_in(i, lambda: buf.copy_(src[i], non_blocking=True))
+            pipe.compute(i, lambda: sub(buf, w, bias, out=res.view(world * rows, Nl)))
+            pipe.copy_out(i, copy_out)
+        pipe.end()
+        return out_host
+
+    def close(self) -> None:
+        """Frees this context's workspaces (collective)."""
+        for sub, _ in getattr(self, "_stream_state", {}).values():
+            if sub is not self and sub.heap is not None:
+                sub.heap.close()
+        self._stream_state = {}
+        if self.heap is not None:
+            self.heap.close()

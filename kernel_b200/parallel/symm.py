@@ -115,6 +115,16 @@ class SymmHeap:
         dist.all_gather_object(flags, bool(ok), group=self.group)
         return all(flags)
 
+    def _agree_or_raise(self, code: int, what: str) -> None:
+        """All ranks learn whether a set-up step worked everywhere: a rank whose
+        step failed raises its own error, the others raise instead of waiting for
+        it in the next barrier until the collective library's time-out."""
+        err = N.last_error() if code != N.KB_OK else ""
+        if not self._all_agree(code == N.KB_OK):
+            if code != N.KB_OK:
+                N.check(code)
+            raise N.NativeError(N.KB_ERR_IO, err or f"a peer failed to {what}")
+
     def _create(self, backend: str, nbytes: int) -> str:
         dev_index = self.device.index if self.device.type == "cuda" else 0
         code = self._lib.kb_symm_create(_BACKENDS[backend], self.rank, self.world, nbytes, dev_index, C.byref(self._h))
@@ -140,18 +150,19 @@ class SymmHeap:
             else:
                 handles[0] = mine.raw
             blob = C.create_string_buffer(b"".join(handles), 64 * self.world)
-            N.check(lib.kb_symm_map_peers(self._h, None, blob))
+            self._agree_or_raise(lib.kb_symm_map_peers(self._h, None, blob), "map the peers' segments")
             return
         fds = (C.c_int * self.world)()
         N.check(
             lib.kb_fd_allgather(session.encode(), b"seg", self.rank, self.world, lib.kb_symm_local_fd(self._h), fds, self.timeout_ms)
         )
         try:
-            N.check(lib.kb_symm_map_peers(self._h, fds, None))
+            code = lib.kb_symm_map_peers(self._h, fds, None)
         finally:
             for fd in fds:
                 if fd >= 0:
                     os.close(fd)
+        self._agree_or_raise(code, "map the peers' segments")
 
     def _setup_multicast(self, session: str) -> None:
         lib = self._lib
@@ -238,6 +249,16 @@ class SymmHeap:
             if st[0] in (1, 2):
                 raise N.SymmTimeoutError(N.KB_ERR_TIMEOUT, msg)
             raise N.NativeError(N.KB_ERR_ARG, msg)
+
+    def agree_epoch(self, epoch: int) -> int:
+        """Collective: the largest ``epoch`` any rank holds.  After a failed call the
+        ranks of a context may have counted different numbers of calls; flags only
+        grow, so everybody continues from the maximum."""
+        if self.world == 1:
+            return epoch
+        vals = [None] * self.world
+        dist.all_gather_object(vals, int(epoch), group=self.group)
+        return max(vals)
 
     def close(self, collective: bool = True) -> None:
         """Unmaps and frees the segments.  Collective by default (a control-plane

@@ -37,6 +37,9 @@ def release_contexts() -> None:
     are freed locally."""
     current = _group()
     for ctx in _contexts.values():
+        for sub, _ in getattr(ctx, "_stream_state", {}).values():  # chunk-sized contexts of run_from_host
+            if sub is not ctx and sub.heap is not None:
+                sub.heap.close(collective=ctx.process_group is current)
         if ctx.heap is not None:
             ctx.heap.close(collective=ctx.process_group is current)
     _contexts.clear()

@@ -40,6 +40,9 @@ def release_contexts() -> None:
     are freed locally."""
     current = _group()
     for ctx in _contexts.values():
+        for sub, _ in getattr(ctx, "_stream_state", {}).values():  # chunk-sized contexts of run_from_host
+            if sub is not ctx and sub.heap is not None:
+                sub.heap.close(collective=ctx.process_group is current)
         if ctx.heap is not None:
             ctx.heap.close(collective=ctx.process_group is current)
     _contexts.clear()
@@ -48,5 +51,5 @@ def release_contexts() -> None:
 def custom_kernel(data: input_t) -> output_t:
     a, w, bias = data
     ctx = get_context(a.shape[0], w.shape[0], a.device)
-    scale = float(ctx.world) if task.get_bias_mode() == "per_rank" else 1.0
+    scale = float(ctx.world) if task.bias_mode_of(data) == "per_rank" else 1.0
     return ctx(a, w, bias, bias_scale=scale)

@@ -3,10 +3,12 @@
 
 Bias convention.  The reference adds the bias on every rank before the
 reduce-scatter (``gemm_rs/reference.py:54-59``), so its result contains
-``world_size * bias``.  ``per_rank`` reproduces that; ``once`` (default) adds the
-bias a single time.  The mode is process-wide state of the task (the data tuple
-keeps the reference's three elements); a test case may select it with the
-``bias_mode`` key, the environment with ``KB200_GEMM_RS_BIAS_MODE``.
+``world_size * bias``.  ``per_rank`` reproduces that and is the default, so that a
+submission written against the reference passes unchanged; ``once`` adds the bias
+a single time.  The mode travels with the data: ``generate_input`` returns a
+``GemmRSInput``, a 3-tuple ``(input, weight, bias)`` like the reference's that also
+carries ``bias_mode``.  A plain tuple means the default, which the environment can
+set with ``KB200_GEMM_RS_BIAS_MODE``; nothing is kept in process-wide state.
 """
 import os
 from typing import Optional, Tuple, TypedDict, TypeVar
@@ -16,18 +18,37 @@ import torch
 input_t = TypeVar("input_t", bound=Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]])
 output_t = TypeVar("output_t", bound=torch.Tensor)
 
-_bias_mode = os.environ.get("KB200_GEMM_RS_BIAS_MODE", "once")
+BIAS_MODES = ("once", "per_rank")
 
 
-def set_bias_mode(mode: str) -> None:
-    global _bias_mode
-    if mode not in ("once", "per_rank"):
-        raise ValueError(f"bias_mode must be 'once' or 'per_rank', got {mode!r}")
-    _bias_mode = mode
+def default_bias_mode() -> str:
+    mode = os.environ.get("KB200_GEMM_RS_BIAS_MODE", "per_rank")
+    if mode not in BIAS_MODES:
+        raise ValueError(f"KB200_GEMM_RS_BIAS_MODE must be one of {BIAS_MODES}, got {mode!r}")
+    return mode
 
 
-def get_bias_mode() -> str:
-    return _bias_mode
+class GemmRSInput(tuple):
+    """``(input, weight, bias)`` plus the bias convention of this case."""
+
+    def __new__(cls, items, bias_mode: Optional[str] = None):
+        self = super().__new__(cls, items)
+        if len(self) != 3:
+            raise ValueError("GemmRSInput holds (input, weight, bias)")
+        mode = bias_mode if bias_mode is not None else default_bias_mode()
+        if mode not in BIAS_MODES:
+            raise ValueError(f"bias_mode must be one of {BIAS_MODES}, got {mode!r}")
+        self.bias_mode = mode
+        return self
+
+    def rebuilt(self, items):
+        """The same case around other tensors (clones, tensors on another device)."""
+        return GemmRSInput(items, self.bias_mode)
+
+
+def bias_mode_of(data) -> str:
+    """Bias convention of a data tuple; a plain tuple has the default."""
+    return getattr(data, "bias_mode", None) or default_bias_mode()
 
 
 class TestSpec(TypedDict, total=False):

@@ -25,13 +25,14 @@ A2A_SHAPES = [  # tokens per rank, hidden, top-k, experts
     (1, 7168, 8, 256), (16, 7168, 8, 256), (128, 7168, 8, 256), (256, 7168, 8, 256), (512, 7168, 8, 256),
     (1024, 7168, 8, 256), (128, 2048, 4, 64), (256, 4096, 8, 256), (1024, 2048, 8, 64),
 ]
-GEMM_RS_SHAPES = [  # m, n, k (k sharded)
+GEMM_RS_SHAPES = [  # m, n, k (k sharded); the first three are the small-M cases the reference ranks (gemm_rs/task.yml:79-81)
+    (64, 7168, 18432), (512, 4096, 12288), (2048, 2880, 2880),
     (1024, 4096, 4096), (4096, 4096, 4096), (8192, 4096, 14336), (8192, 8192, 29568), (16384, 8192, 8192),
 ]
 AG_GEMM_SHAPES = [  # m, n (n sharded), k
     (1024, 4096, 4096), (4096, 14336, 4096), (8192, 29568, 8192), (16384, 29568, 4096),
 ]
-QUICK = {"a2a": [0, 3], "gemm_rs": [1, 3], "ag_gemm": [0, 2]}
+QUICK = {"a2a": [0, 3], "gemm_rs": [4, 6], "ag_gemm": [0, 2]}
 
 
 def main() -> int:
@@ -43,16 +44,21 @@ def main() -> int:
     ap.add_argument("--out", default=None)
     ap.add_argument("--timing-words", action="store_true",
                     help="GEMM ops: also report the kernel's timing words (us waited on peers, us until pushes were out, "
-                         "us until the last epilogue; maximum over CTAs, calls and ranks)")
+                         "us until the last epilogue or reduction; maximum over CTAs, calls and ranks)")
     ns = ap.parse_args()
 
     if ns.timing_words:
-        os.environ["KB200_GEMM_DEBUG"] = "8"
+        os.environ["KB200_GEMM_TIMING"] = "1"  # read once, by the library's first GEMM launch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29577")
+    if "MASTER_PORT" not in os.environ:  # single process without a launcher: any free port
+        import socket
+
+        with socket.socket() as sock:
+            sock.bind(("127.0.0.1", 0))
+            os.environ["MASTER_PORT"] = str(sock.getsockname()[1])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -133,7 +139,7 @@ def main() -> int:
         for (m, n, k) in pick("gemm_rs", GEMM_RS_SHAPES):
             if m % world or k % world or (k // world) % 8:
                 continue
-            data = rs_ref.generate_input(rank, world, m, n, k, True, 3, dist="normal")
+            data = rs_ref.generate_input(rank, world, m, n, k, True, 3, dist="normal", bias_mode="once")
             out = rs_sub.custom_kernel(data)
             ok, msg = rs_ref.check_implementation(data, out)
             ctx = rs_sub.get_context(m, n, dev)

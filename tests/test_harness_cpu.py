@@ -139,3 +139,23 @@ def test_submission_given_as_a_file_path(tmp_path):
     assert log["check"] == "pass"
     rc, log, err = _run(["test", "@tests", "--backend", "gloo", "--submission", str(tmp_path / "absent.py")], RS + "\n", tmp_path)
     assert rc == 112 and "not found" in log["test.0.error"]
+
+
+def test_a_case_that_runs_out_of_time_does_not_block_the_next_one(tmp_path):
+    """The first case never returns on rank 1; its workers are terminated and
+    replaced, so the second case still runs (and passes) in fresh processes."""
+    (tmp_path / "stuck_sub.py").write_text(
+        "import time\n"
+        "import torch.distributed as dist\n"
+        "from kernel_b200.tasks.gemm_rs.submission import custom_kernel as good\n"
+        "def custom_kernel(data):\n"
+        "    if data[0].shape[0] == 128 and dist.get_rank() == 1:\n"
+        "        time.sleep(600)\n"
+        "    return good(data)\n")
+    stuck = "world_size: 2; m: 128; n: 128; k: 256; has_bias: False; seed: 3"
+    rc, log, err = _run(["test", "@tests", "--backend", "gloo", "--submission", "stuck_sub"], stuck + "\n" + RS + "\n", tmp_path,
+                        env_extra={"PYTHONPATH": f"{ROOT}:{tmp_path}", "KB200_EVAL_TEST_TIMEOUT_S": "20",
+                                   "KB200_WAIT_LIMIT_MS": "3000"})
+    assert rc == 112 and log["check"] == "fail"
+    assert log["test.0.status"] == "fail" and "timed out" in log["test.0.error"]
+    assert log["test.1.status"] == "pass"

@@ -123,6 +123,98 @@ def test_ag_gemm_shapes():
             assert repeat
 
 
+def _nvls_bring_up(rank, world):
+    """Multicast object over a 1 MB buffer: create, add, bind, multimem.st from every
+    rank, every rank reads all slices; then a multimem.ld_reduce over all ranks' copies;
+    unbind and close in order with all ranks alive."""
+    import torch
+
+    from kernel_b200 import _native as N
+    from kernel_b200.parallel.symm import SymmHeap
+
+    dev = torch.device("cuda", rank)
+    heap = SymmHeap(4 << 20, device=dev, nvls=True)
+    if heap.mc_ptr is None:
+        heap.close()
+        return "no multicast"
+    lib = N.lib()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    nbytes = 1 << 20
+    piece = nbytes // world // 16 * 16
+    off = heap.alloc(nbytes)
+    src = torch.full((piece // 2,), float(rank + 1), dtype=torch.bfloat16, device=dev)
+    N.check(lib.kb_multimem_store(heap.mc_ptr + off + rank * piece, src.data_ptr(), piece, stream))
+    heap.barrier()
+    torch.cuda.synchronize()
+    got = heap.tensor(off, (world, piece // 2), torch.bfloat16)
+    stored = all(bool((got[r] == r + 1).all()) for r in range(world))
+    off2 = heap.alloc(nbytes)
+    heap.tensor(off2, (nbytes // 2,), torch.bfloat16).fill_(float(rank + 1))
+    heap.barrier()
+    total = torch.empty(nbytes // 2, dtype=torch.bfloat16, device=dev)
+    N.check(lib.kb_multimem_reduce_bf16(total.data_ptr(), heap.mc_ptr + off2, nbytes, stream))
+    torch.cuda.synchronize()
+    reduced = bool((total == world * (world + 1) // 2).all())
+    heap.barrier()  # nobody unbinds while a peer's load may still be in the switch
+    torch.cuda.synchronize()
+    heap.check_status()
+    heap.close()
+    return stored, reduced
+
+
+def test_nvls_multicast_bring_up():
+    world = _world()
+    res = run_ranks(_nvls_bring_up, world, backend="nccl", timeout=180)
+    if all(r == "no multicast" for r in res):
+        pytest.skip("the devices or the driver offer no multicast objects")
+    assert all(r == (True, True) for r in res), res
+
+
+def _fused_gemms_over_nvls(rank, world):
+    """The reduce-scatter pull through multimem.ld_reduce and the all-gather push
+    through multimem.st, checked by the tasks' oracles."""
+    import torch
+
+    from kernel_b200.tasks.ag_gemm import reference as AR
+    from kernel_b200.tasks.ag_gemm import submission as AS
+    from kernel_b200.tasks.gemm_rs import reference as RR
+    from kernel_b200.tasks.gemm_rs import submission as RS
+
+    res = []
+    for (m, n, k, bias) in [(64, 2880, 2880 // 8 * world, True), (2048, 4096, 7168 // 8 * world, True),
+                            (8192, 8192, 29568 // 8 * world, True)]:
+        data = RR.generate_input(rank, world, m, n, k, bias, seed=7, dist="normal", bias_mode="once")
+        out = RS.custom_kernel(data)
+        out2 = RS.custom_kernel(data)
+        torch.cuda.synchronize()
+        ctx = RS.get_context(m, n, data[0].device)
+        ctx.heap.check_status()
+        ok, msg = RR.check_implementation(data, out)
+        res.append(("gemm_rs", ctx.heap.mc_ptr is not None, ok and bool(torch.equal(out, out2)), msg))
+    for (m, n, k, bias) in [(64, 2880, 2880, True), (1024, 4096, 4096, False), (8192, 3696 * world, 8192, True)]:
+        data = AR.generate_input(rank, world, m, n, k, bias, seed=9)
+        out = AS.custom_kernel(data)
+        out2 = AS.custom_kernel(data)
+        torch.cuda.synchronize()
+        ctx = AS.get_context(m, k, data[0].device)
+        ctx.heap.check_status()
+        ok, msg = AR.check_implementation(data, out)
+        res.append(("ag_gemm", ctx.heap.mc_ptr is not None, ok and bool(torch.equal(out, out2)), msg))
+    RS.release_contexts()
+    AS.release_contexts()
+    return res
+
+
+def test_fused_gemms_over_nvls():
+    world = _world()
+    res = run_ranks(_fused_gemms_over_nvls, world, backend="nccl", timeout=300, env={"KB200_NVLS": "1"})
+    if not any(mc for per_rank in res for _, mc, _, _ in per_rank):
+        pytest.skip("the devices or the driver offer no multicast objects")
+    for per_rank in res:
+        for op, mc, ok, msg in per_rank:
+            assert mc and ok, (op, msg)
+
+
 def _mlp_backward(rank, world):
     """Forward + backward of the trainable sequence-parallel MLP; returns the
     relative errors against dense fp32 autograd on the gathered problem."""

@@ -79,7 +79,7 @@ def _gemm_rs(rank, world, bias_mode):
     data = R.generate_input(rank, world, 64, 48, 256, True, 21, dist="normal", bias_mode=bias_mode, device="cpu")
     a, w, bias = data
     assert a.shape == (64, 256 // world) and w.shape == (48, 256 // world) and bias.shape == (48,)
-    assert task.get_bias_mode() == bias_mode
+    assert task.bias_mode_of(data) == bias_mode and task.bias_mode_of((a, w, bias)) == "per_rank"  # plain tuple: default
     shards_a, shards_w = [None] * world, [None] * world
     dist.all_gather_object(shards_a, a)
     dist.all_gather_object(shards_w, w)

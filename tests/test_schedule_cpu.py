@@ -1,6 +1,7 @@
 """The GEMM kernels' static tile schedule, checked on the host replica of the
-device function: every tile exactly once, the rows a rank owns last for the
-reduce-scatter, own rows first and arrival order after that for the all-gather."""
+device function: every tile exactly once, block c of every owner before block
+c+1 of any owner for the reduce-scatter, own rows first and arrival order after
+that for the all-gather."""
 import ctypes as C
 
 import pytest
@@ -38,20 +39,25 @@ def test_every_tile_exactly_once(mode, M, Nn, world, pair):
         assert all(0 <= b < mbq and 0 <= n < nbs for b, n in tiles)
 
 
+def _first_appearances(tiles):
+    seq = []
+    for b, _ in tiles:
+        if b not in seq:
+            seq.append(b)
+    return seq
+
+
 @pytest.mark.parametrize("pair", [False, True])
-def test_reduce_scatter_visits_own_rows_last(pair):
+def test_reduce_scatter_visits_block_c_of_every_owner_before_block_c_plus_1(pair):
     M, Nn, world = 8192, 8192, 8
     rows = 256 if pair else 128
     per_rank = M // world // rows
-    nbs = Nn // 256
     for rank in range(world):
-        tiles = schedule(RS, M, Nn, rank, world, pair)
-        own = set(range(rank * per_rank, (rank + 1) * per_rank))
-        tail = tiles[-per_rank * nbs:]
-        assert {b for b, _ in tail} == own
-        assert not ({b for b, _ in tiles[:-per_rank * nbs]} & own)
-        # the sweep starts with the rows of the next rank, so that every owner is fed by a different peer
-        assert tiles[0][0] == ((rank + 1) % world) * per_rank
+        seq = _first_appearances(schedule(RS, M, Nn, rank, world, pair))
+        assert [b % per_rank for b in seq] == sorted(b % per_rank for b in seq)   # chunk-major on every rank
+        for c in range(per_rank):
+            owners = [b // per_rank for b in seq[c * world:(c + 1) * world]]
+            assert owners == [(rank + 1 + d) % world for d in range(world)]         # ring order, own block last
 
 
 def test_small_m_reduce_scatter_single_block_holds_all_owners():
@@ -81,8 +87,9 @@ def test_all_gather_order_own_first_then_arrival_order(pair):
 
 def test_schedule_properties_over_random_problems():
     """Random shapes, world sizes and tile configurations: every tile exactly once; for
-    the reduce-scatter no tile holding rows of this rank comes before a tile that
-    holds none; for the all-gather the first row block visited holds own rows."""
+    the reduce-scatter the blocks appear chunk by chunk (block c of every owner before
+    block c+1 of any) when blocks do not straddle owners; for the all-gather the first
+    row block visited holds own rows."""
     from hypothesis import given, settings
     from hypothesis import strategies as st
 
@@ -109,8 +116,9 @@ def test_schedule_properties_over_random_problems():
             lo, hi = rank * rpo, (rank + 1) * rpo - 1                  # rows of this rank
             own = [lo // rows <= b <= hi // rows for b, _ in tiles]
             if mode == RS:
-                first_own = own.index(True)
-                assert all(own[first_own:])                            # own segment is a suffix
+                if rpo % rows == 0:
+                    chunk = [b % (rpo // rows) for b in _first_appearances(tiles)]
+                    assert chunk == sorted(chunk)                      # chunk-major
             else:
                 assert own[0]                                          # the all-gather starts on rows it already has
 
