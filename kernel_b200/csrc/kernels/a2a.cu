@@ -195,8 +195,8 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh, i
   int32_t* tot = sh;               // [E] entries per expert, whole rank
   int32_t* pre = tot + p.E;        // [E] entries per expert before this CTA's tokens
   int32_t* off = pre + p.E;        // [E] first slot of the expert inside its owner's region
-  int32_t* ent_e = off + p.E;      // [MAX_ENT_PER_CTA]
-  int32_t* ent_slot = ent_e + MAX_ENT_PER_CTA;
+  int32_t* ent_e = off + p.E;      // [MAX_ENT_PER_CTA] expert of each (token, k) entry of this CTA's tokens
+  int32_t* ent_slot = ent_e + MAX_ENT_PER_CTA;  // [MAX_ENT_PER_CTA] its row in the owner's region, or -1
 
   const int tid = threadIdx.x;
   stamp(p, ST_ENTRY);
@@ -210,17 +210,17 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh, i
     pre[e] = 0;
   }
   __syncthreads();
-  // Eight entries per thread are fetched before any is counted: one memory
-  // latency per eight entries instead of one per entry.
-  for (int i0 = tid; i0 < total_ent; i0 += 8 * blockDim.x) {
-    int ev[8];
+  // Sixteen entries per thread are fetched before any is counted: one memory
+  // latency per sixteen entries instead of one per entry.
+  for (int i0 = tid; i0 < total_ent; i0 += 16 * blockDim.x) {
+    int ev[16];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
+    for (int u = 0; u < 16; ++u) {
       const int i = i0 + u * blockDim.x;
       ev[u] = i < total_ent ? __ldg(p.idx + i) : 0;
     }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
+    for (int u = 0; u < 16; ++u) {
       const int i = i0 + u * blockDim.x;
       if (i >= total_ent) continue;
       const int e = ev[u];
@@ -403,34 +403,50 @@ __device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh, int
     __syncthreads();
     const int rows = incl[p.El - 1];
     const int first = static_cast<int>((blockIdx.x + 37u * static_cast<unsigned>(s)) % static_cast<unsigned>(nworkers));
-    for (int row = first; row < rows; row += nworkers) {
-      // first local expert whose inclusive prefix exceeds row
-      int lo = 0, hi = p.El - 1;
-      while (lo < hi) {
-        const int mid = (lo + hi) >> 1;
-        if (incl[mid] > row) hi = mid; else lo = mid + 1;
-      }
-      float scale = 1.0f;
-      if (p.scale_mode == 1) scale = static_cast<float>(1 + p.rank);
-      if (p.scale_mode == 2) scale = static_cast<float>(p.rank * p.El + lo + 1) / static_cast<float>(p.E);
-      const uint4* src = reinterpret_cast<const uint4*>(rows_ptr(p, p.rank, p.recv_off, s, row));
-      uint4* dst = reinterpret_cast<uint4*>(rows_ptr(p, p.rank, p.y_off, s, row));
-      for (int vb = tid; vb < p.vecs; vb += 4 * blockDim.x) {
-        uint4 in[4];
+    // Two rows of this CTA per step: up to eight 16-byte loads per thread in flight.
+    for (int rowA = first; rowA < rows; rowA += 2 * nworkers) {
+      int rowv[2] = {rowA, rowA + nworkers};
+      float scale[2];
+      const uint4* src[2];
+      uint4* dst[2];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {  // all loads of this thread first: one latency per row
-          const int v = vb + u * blockDim.x;
-          if (v < p.vecs) in[u] = kb::ld_sys_v4(src + v);
+      for (int b = 0; b < 2; ++b) {
+        if (rowv[b] >= rows) rowv[b] = -1;
+        const int row = rowv[b] < 0 ? rowA : rowv[b];
+        // first local expert whose inclusive prefix exceeds row
+        int lo = 0, hi = p.El - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi) >> 1;
+          if (incl[mid] > row) hi = mid; else lo = mid + 1;
+        }
+        scale[b] = 1.0f;
+        if (p.scale_mode == 1) scale[b] = static_cast<float>(1 + p.rank);
+        if (p.scale_mode == 2) scale[b] = static_cast<float>(p.rank * p.El + lo + 1) / static_cast<float>(p.E);
+        src[b] = reinterpret_cast<const uint4*>(rows_ptr(p, p.rank, p.recv_off, s, row));
+        dst[b] = reinterpret_cast<uint4*>(rows_ptr(p, p.rank, p.y_off, s, row));
+      }
+      for (int vb = tid; vb < p.vecs; vb += 4 * blockDim.x) {
+        uint4 in[2][4];
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {  // all loads of this thread first: one latency per pair of rows
+            const int v = vb + u * blockDim.x;
+            if (rowv[b] >= 0 && v < p.vecs) in[b][u] = kb::ld_sys_v4(src[b] + v);
+          }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int v = vb + u * blockDim.x;
-          if (v < p.vecs) {
-            float f[Vec16<T>::N];
-            Vec16<T>::load(in[u], f);
+        for (int b = 0; b < 2; ++b) {
 #pragma unroll
-            for (int i = 0; i < Vec16<T>::N; ++i) f[i] *= scale;
-            dst[v] = Vec16<T>::store(f);
+          for (int u = 0; u < 4; ++u) {
+            const int v = vb + u * blockDim.x;
+            if (rowv[b] >= 0 && v < p.vecs) {
+              float f[Vec16<T>::N];
+              Vec16<T>::load(in[b][u], f);
+#pragma unroll
+              for (int i = 0; i < Vec16<T>::N; ++i) f[i] *= scale[b];
+              dst[b][v] = Vec16<T>::store(f);
+            }
           }
         }
       }
@@ -453,9 +469,27 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_expert_kernel(const A2aParams
 }
 
 // ------------------------------------------------------------------- combine ----
+// `ent_e` / `ent_slot` hold expert and slot of the (token, k) entries of this
+// CTA's tokens in shared memory: left there by the dispatch phase of a fused
+// launch, or loaded by the prologue below when the combine runs as a launch of
+// its own.  The k rows of a token are pulled with peer loads, two 16-byte
+// vectors per thread and iteration (up to sixteen loads in flight), and
+// accumulated in fp32 in fixed k order.
 template <typename T, bool kFused>
-__device__ __forceinline__ void combine_body(const A2aParams& p) {
+__device__ __forceinline__ void combine_body(const A2aParams& p, int32_t* ent_e, int32_t* ent_slot) {
   const int tid = threadIdx.x;
+  int t0, t1, v0, v1, hs;
+  unit_ranges(p, t0, t1, v0, v1, hs);
+  if (!kFused) {
+    const int n_ent = (t1 - t0) * p.k;
+    for (int i = tid; i < n_ent; i += blockDim.x) {
+      const int e = p.idx[t0 * p.k + i];
+      const int slot = p.slots[t0 * p.k + i];
+      const bool ok = e >= 0 && e < p.E && slot >= 0 && slot < p.cap;
+      ent_e[i] = ok ? e : 0;
+      ent_slot[i] = ok ? slot : -1;
+    }
+  }
   const uint64_t w0 = (p.trace != nullptr && blockIdx.x == 0 && tid == 0) ? kb::globaltimer_ns() : 0;
   if (tid < p.world) {
     if (!wait_arrival<kFused>(p, 1, tid)) {
@@ -465,11 +499,10 @@ __device__ __forceinline__ void combine_body(const A2aParams& p) {
   __syncthreads();
   if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) p.trace[ST_WAITED_COMBINE] = kb::globaltimer_ns() - w0;
   stamp(p, ST_COMBINE_GO);
-  int t0, t1, v0, v1, hs;
-  unit_ranges(p, t0, t1, v0, v1, hs);
-  // Two 16-byte vectors per thread and iteration: up to sixteen peer loads in
-  // flight, accumulated in fixed k order.
   for (int t = t0; t < t1; ++t) {
+    const int32_t* te = ent_e + (t - t0) * p.k;
+    const int32_t* ts = ent_slot + (t - t0) * p.k;
+    const float* tw = p.w + static_cast<size_t>(t) * p.k;
     for (int vb = v0 + tid; vb < v1; vb += 2 * blockDim.x) {
       float acc[2][Vec16<T>::N];
 #pragma unroll
@@ -485,15 +518,11 @@ __device__ __forceinline__ void combine_body(const A2aParams& p) {
           const int kk = k0 + j;
           wk[j] = 0.f;
           u[0][j] = u[1][j] = make_uint4(0, 0, 0, 0);
-          if (kk < p.k) {
-            const int e = p.idx[t * p.k + kk];
-            const int slot = p.slots[t * p.k + kk];
-            if (e >= 0 && e < p.E && slot >= 0 && slot < p.cap) {
-              wk[j] = p.w[t * p.k + kk];
-              const uint4* row = reinterpret_cast<const uint4*>(rows_ptr(p, e / p.El, p.y_off, p.rank, slot));
-              u[0][j] = kb::ld_sys_v4(row + vb);
-              if (vb + blockDim.x < v1) u[1][j] = kb::ld_sys_v4(row + vb + blockDim.x);
-            }
+          if (kk < p.k && ts[kk] >= 0) {
+            wk[j] = __ldg(tw + kk);
+            const uint4* row = reinterpret_cast<const uint4*>(rows_ptr(p, te[kk] / p.El, p.y_off, p.rank, ts[kk]));
+            u[0][j] = kb::ld_sys_v4(row + vb);
+            if (vb + blockDim.x < v1) u[1][j] = kb::ld_sys_v4(row + vb + blockDim.x);
           }
         }
 #pragma unroll
@@ -517,7 +546,8 @@ __device__ __forceinline__ void combine_body(const A2aParams& p) {
 
 template <typename T>
 __global__ void __launch_bounds__(A2A_THREADS) a2a_combine_kernel(const A2aParams p) {
-  combine_body<T, false>(p);
+  extern __shared__ int32_t sh[];
+  combine_body<T, false>(p, sh, sh + MAX_ENT_PER_CTA);
 }
 
 // All three phases in one cooperative launch (every CTA is resident, so CTAs may
@@ -535,9 +565,9 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_fused_kernel(const A2aParams 
   }
   dispatch_body(p, sh, nworkers);
   __syncthreads();
-  expert_body<T, true>(p, sh, nworkers);
+  expert_body<T, true>(p, sh, nworkers);  // uses the first experts-per-rank words only: the entry tables stay intact
   __syncthreads();
-  combine_body<T, true>(p);
+  combine_body<T, true>(p, sh + 3 * p.E, sh + 3 * p.E + MAX_ENT_PER_CTA);
 }
 
 // --------------------------------------------------------------- small utils ----
@@ -735,11 +765,12 @@ extern "C" int kb_a2a_combine(const KbA2aArgs* a, void* stream) {
   rc = fill_params(a, &p, sms);
   if (rc != KB_OK) return rc;
   const int want = p.tok_groups * p.h_splits;
+  const size_t smem = 2 * MAX_ENT_PER_CTA * sizeof(int32_t);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (a->dtype) {
-    case 0: a2a_combine_kernel<__nv_bfloat16><<<want, A2A_THREADS, 0, st>>>(p); break;
-    case 1: a2a_combine_kernel<__half><<<want, A2A_THREADS, 0, st>>>(p); break;
-    case 2: a2a_combine_kernel<float><<<want, A2A_THREADS, 0, st>>>(p); break;
+    case 0: a2a_combine_kernel<__nv_bfloat16><<<want, A2A_THREADS, smem, st>>>(p); break;
+    case 1: a2a_combine_kernel<__half><<<want, A2A_THREADS, smem, st>>>(p); break;
+    case 2: a2a_combine_kernel<float><<<want, A2A_THREADS, smem, st>>>(p); break;
     default: kb::set_error("a2a: unknown dtype %d", a->dtype); return KB_ERR_ARG;
   }
   KB_CUDA_OK(cudaGetLastError());

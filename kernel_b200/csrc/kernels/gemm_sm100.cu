@@ -22,11 +22,14 @@
 // Mainloop: one TMA producer thread fills a ring of 128x64 (A) and 256x64 (B)
 // K-major tiles with 128-byte swizzle; one thread issues tcgen05.mma into one of
 // two 256-column TMEM accumulators; four epilogue warps drain the other
-// accumulator.  PLAIN and AG write the output with TMA stores (tcgen05.ld ->
+// accumulator.  Two epilogue variants: "tma" (PLAIN and AG only) goes tcgen05.ld ->
 // bf16 -> 128-byte-swizzled shared memory -> cp.async.bulk.tensor store issued
-// by one lane per warp, two staging buffers per warp); RS writes the staging
-// matrix with 16-byte row-contiguous stores, whose ordering against the flag
-// release is that of ordinary stores.
+// by one lane per warp, two staging boxes per warp; "direct" stores 16-byte
+// vectors straight from the registers tcgen05.ld filled (a lane owns a row, so a
+// warp's store touches 32 rows: more L2 transactions for the output, which is a
+// few percent of the kernel's traffic) and needs no staging memory, which buys
+// the CTA-pair configuration a seventh pipeline stage.  RS always stores
+// directly: its stores must be ordered before a flag release as ordinary stores.
 //
 // The op replaces torch.matmul + bias add + reduce_scatter_tensor of the
 // reference (gemm_rs/reference.py:49-60, gemm_rs/submission.py:23-28).
@@ -53,27 +56,26 @@ constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
 // Single CTA: 128x256 tile, B stage = 256 rows, 4 stages of 48 KB.
 // CTA pair (cta_group::2): 256x256 tile over two SMs, each CTA stages its 128
-// rows of A and its 128 of the 256 B rows: 6 stages of 32 KB.
-template <bool kPair>
+// rows of A and its 128 of the 256 B rows: 6 stages of 32 KB, 7 when the
+// epilogue needs no staging memory.
+template <bool kPair, bool kDirect>
 struct Cfg {
-  static constexpr int STAGES = kPair ? 6 : 4;
+  static constexpr int STAGES = kPair ? (kDirect ? 7 : 6) : 4;
   static constexpr int B_ROWS = kPair ? 128 : 256;
   static constexpr int B_BYTES = B_ROWS * BK * 2;
 };
-constexpr int MAX_STAGES = 6;
-// Epilogue staging: 8 KB per warp.  RS: 32 rows x 128 columns (256-byte rows,
-// 16-byte chunks XOR-swizzled by row).  PLAIN/AG: two buffers of 32 rows x 64
-// columns in the 128-byte-swizzle layout of the output tensor map.
-constexpr int EPI_COLS = 128;
-constexpr int EPI_ROW_BYTES = EPI_COLS * 2;
-constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;
+constexpr int MAX_STAGES = 7;
+// Staging of the "tma" epilogue: per warp two boxes of 32 rows x 64 columns in
+// the 128-byte-swizzle layout of the output tensor map.
+constexpr int EPI_WARP_BYTES = 8192;
 constexpr int EPI_BYTES = 4 * EPI_WARP_BYTES;
+static_assert(6 * 32768 + EPI_BYTES <= 7 * 32768, "six pair stages plus the staging boxes fit where seven stages fit");
 constexpr int OUT_BOX_COLS = 64;
 constexpr int OUT_BOX_ROWS = 32;
 constexpr int OUT_BOX_BYTES = OUT_BOX_ROWS * OUT_BOX_COLS * 2;  // 4 KB
 constexpr int TMEM_COLS = 512;
 constexpr int BAR_BYTES = 256;
-constexpr int SMEM_BYTES = 1024 + 4 * (A_BYTES + 32768) + EPI_BYTES + BAR_BYTES;  // same total for both configurations
+constexpr int SMEM_BYTES = 1024 + 7 * 32768 + BAR_BYTES;  // 6 pair stages + staging = 4 single stages + staging = 7 pair stages
 constexpr int THREADS_BASE = 256;             // warps 0..3 control, 4..7 epilogue
 constexpr int THREADS_COMM = 384;             // + warps 8..11: all-gather pushers or reduce-scatter reducers
 constexpr int RS_ROW_GROUP = 64;              // rows of one reduction unit
@@ -128,15 +130,15 @@ struct Smem {
   volatile uint32_t* abort;
 };
 
-template <bool kPair>
+template <bool kPair, bool kDirect>
 __device__ __forceinline__ Smem carve(uint8_t* raw) {
-  constexpr int STAGES = Cfg<kPair>::STAGES;
+  constexpr int STAGES = Cfg<kPair, kDirect>::STAGES;
   Smem s;
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   s.a = base;
   s.b = base + STAGES * A_BYTES;
-  s.epi = s.b + STAGES * Cfg<kPair>::B_BYTES;  // 1024-byte aligned: every stage is a multiple of 1024 bytes
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s.epi + EPI_BYTES);
+  s.epi = s.b + STAGES * Cfg<kPair, kDirect>::B_BYTES;  // 1024-byte aligned: every stage is a multiple of 1024 bytes
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + 7 * 32768);  // behind the largest configuration
   s.full = bars;
   s.empty = bars + MAX_STAGES;
   s.tfull = bars + 2 * MAX_STAGES;
@@ -244,20 +246,20 @@ __device__ __forceinline__ uint4 cvt8(const uint32_t* r, const bf16* bias, float
   return pack8(f);
 }
 
-// TMEM -> bf16 -> this warp's 32 x 128 staging rows (16-byte chunks XOR-swizzled
-// by row so both the row-per-thread writes and the row-contiguous reads are
-// bank-conflict free).
-__device__ __forceinline__ void stage_half(uint32_t taddr, uint8_t* warp_epi, int lane) {
+// TMEM -> bf16 (+ bias) -> global memory, 64 columns of this lane's row: eight
+// 16-byte stores straight from the registers.
+__device__ __forceinline__ void store_direct(uint32_t taddr, bf16* row_ptr, bool row_ok, const bf16* bias, float bias_scale,
+                                             int col0, int n_cols) {
 #pragma unroll
-  for (int c = 0; c < EPI_COLS / 32; ++c) {
+  for (int c = 0; c < 2; ++c) {
     uint32_t r[32];
     kb::tmem_ld_32x32(taddr + c * 32, r);
     kb::tmem_ld_wait();
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint4 v = cvt8(r + 8 * i, nullptr, 0.f, 0, 0);
-      const int j = c * 4 + i;
-      *reinterpret_cast<uint4*>(warp_epi + lane * EPI_ROW_BYTES + ((j ^ (lane & 15)) * 16)) = v;
+      const int col = col0 + (c * 4 + i) * 8;
+      const uint4 v = cvt8(r + 8 * i, bias, bias_scale, col, n_cols);
+      if (row_ok && col < n_cols) *reinterpret_cast<uint4*>(row_ptr + col) = v;
     }
   }
 }
@@ -280,13 +282,14 @@ __device__ __forceinline__ void stage_box(uint32_t taddr, uint8_t* box, int lane
   }
 }
 
-template <int kMode, bool kPair>
+template <int kMode, bool kPair, bool kDirect>
 __global__ void __launch_bounds__(kMode == KB_GEMM_PLAIN ? THREADS_BASE : THREADS_COMM, 1)
 gemm_kernel(const __grid_constant__ GemmParams p) {
   constexpr bool kAG = (kMode == KB_GEMM_AG);
   constexpr bool kRS = (kMode == KB_GEMM_RS);
-  constexpr int STAGES = Cfg<kPair>::STAGES;
-  constexpr int B_BYTES = Cfg<kPair>::B_BYTES;
+  static_assert(!kRS || kDirect, "the reduce-scatter epilogue stores directly");
+  constexpr int STAGES = Cfg<kPair, kDirect>::STAGES;
+  constexpr int B_BYTES = Cfg<kPair, kDirect>::B_BYTES;
   // In a pair the even CTA leads: it issues the MMAs for both and owns the
   // barriers the MMA issuer waits on.
   const uint32_t cta_rank = kPair ? kb::cluster_ctarank() : 0u;
@@ -294,7 +297,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
   const int sched_id = kPair ? (blockIdx.x >> 1) : blockIdx.x;
   const int sched_n = kPair ? (gridDim.x >> 1) : gridDim.x;
   extern __shared__ uint8_t smem_raw[];
-  Smem sm = carve<kPair>(smem_raw);
+  Smem sm = carve<kPair, kDirect>(smem_raw);
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -326,7 +329,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     kb::tma_prefetch_desc(&p.tmA);
     kb::tma_prefetch_desc(&p.tmB);
     if (kAG && p.ag_own_direct) kb::tma_prefetch_desc(&p.tmOwn);
-    if (!kRS) kb::tma_prefetch_desc(&p.tmOut);
+    if (!kDirect) kb::tma_prefetch_desc(&p.tmOut);
   }
   kb::tc_fence_before_sync();
   __syncthreads();
@@ -491,7 +494,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
       const int row0 = mb * BM;
 
-      if constexpr (!kRS) {
+      if constexpr (!kDirect) {
         // Four passes of 64 columns through two staging boxes; lane 0 owns the
         // bulk groups of this warp.  A box is rewritten only after the store that
         // last read it has finished reading (at most one younger group pending).
@@ -512,38 +515,31 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           }
         }
       } else {
-        // Reduce-scatter: the whole tile goes, as bf16, into this rank's own
-        // staging matrix; then the owners of its rows are told.
-        bf16* stage = reinterpret_cast<bf16*>(p.peer_base[p.rank] + p.data_off);
+        // A lane owns row (32 q + lane) of the tile and stores it 16 bytes at a
+        // time.  RS: the row goes, without bias, into this rank's own staging
+        // matrix (the partial product); then the owners of the tile's rows are told.
+        const int gr = row0 + q * 32 + lane;
+        bf16* row_ptr = kRS ? reinterpret_cast<bf16*>(p.peer_base[p.rank] + p.data_off) + rs_stage_elem(p, gr < p.M ? gr : 0)
+                            : p.out + static_cast<size_t>(gr < p.M ? gr : 0) * p.N;
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-          stage_half(taddr + h * EPI_COLS, warp_epi, lane);
-          if (h == 1) release_acc(acc);
-          __syncwarp();
-          const int j = lane & 15;
-          const int col = nb * BN + h * EPI_COLS + j * 8;
-#pragma unroll 4
-          for (int i = 0; i < 16; ++i) {
-            const int row = i * 2 + (lane >> 4);
-            const int gr = row0 + q * 32 + row;
-            if (gr < p.M && col < p.N) {
-              const uint4 v = *reinterpret_cast<const uint4*>(warp_epi + row * EPI_ROW_BYTES + ((j ^ (row & 15)) * 16));
-              *reinterpret_cast<uint4*>(stage + rs_stage_elem(p, gr) + col) = v;
-            }
-          }
-          __syncwarp();
+        for (int ps = 0; ps < BN / OUT_BOX_COLS; ++ps) {
+          store_direct(taddr + ps * OUT_BOX_COLS, row_ptr, gr < p.M, kRS ? nullptr : p.bias, p.bias_scale,
+                       nb * BN + ps * OUT_BOX_COLS, p.N);
         }
-        epi_bar_sync();
-        if (et == 0 && row0 < p.M) {
-          int last_row = row0 + BM - 1;
-          if (last_row > p.M - 1) last_row = p.M - 1;
-          const int tile_id = mb * p.NB + nb;
-          kb::fence_sys();
-          for (int o = row0 / p.rpo; o <= last_row / p.rpo; ++o) kb::st_relaxed_sys_u32(rs_flag(p, o, p.rank, tile_id), p.epoch);
+        release_acc(acc);
+        if constexpr (kRS) {
+          epi_bar_sync();
+          if (et == 0 && row0 < p.M) {
+            int last_row = row0 + BM - 1;
+            if (last_row > p.M - 1) last_row = p.M - 1;
+            const int tile_id = mb * p.NB + nb;
+            kb::fence_sys();
+            for (int o = row0 / p.rpo; o <= last_row / p.rpo; ++o) kb::st_relaxed_sys_u32(rs_flag(p, o, p.rank, tile_id), p.epoch);
+          }
         }
       }
     }
-    if constexpr (!kRS) {
+    if constexpr (!kDirect) {
       if (lane == 0) kb::bulk_wait_group<0>();  // the staging boxes are read and the output is written before the CTA leaves
     }
     if (p.status != nullptr && p.timing && lane == 0 && !kRS) {
@@ -583,32 +579,55 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       const int c0 = nb * BN + half * RS_UNIT_COLS;
       constexpr int VPR = RS_UNIT_COLS / 8;  // 16-byte vectors per unit row
       const int total = (r1 - r0) * VPR;
-      for (int v0 = rt; v0 < total; v0 += 2 * 128) {
-        float accv[2][8];
-        int rowv[2], colv[2];
-        bool live[2];
+      auto finish = [&](float* accv, int row, int col) {
+        if (p.bias != nullptr) {
+          float bz[8];
+          unpack8(*reinterpret_cast<const uint4*>(p.bias + col), bz);
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
-          const int v = v0 + b * 128;
-          rowv[b] = r0 + v / VPR;
-          colv[b] = c0 + (v % VPR) * 8;
-          live[b] = v < total && colv[b] < p.N;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) accv[b][e] = 0.f;
+          for (int e = 0; e < 8; ++e) accv[e] += p.bias_scale * bz[e];
         }
-        if (p.mc_base != nullptr) {
-          uint4 x[2];
+        *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(row - row_begin) * p.N + col) = pack8(accv);
+      };
+      if (p.mc_base != nullptr) {
+        // One multimem.ld_reduce per vector: the switch adds the ranks' values.
+        // Eight vectors per thread in flight.
+        const bf16* mc_stage = reinterpret_cast<const bf16*>(p.mc_base + p.data_off);
+        for (int v0 = rt; v0 < total; v0 += 8 * 128) {
+          uint4 x[8];
 #pragma unroll
-          for (int b = 0; b < 2; ++b) {
+          for (int b = 0; b < 8; ++b) {
+            const int v = v0 + b * 128;
+            const int row = r0 + v / VPR, col = c0 + (v % VPR) * 8;
             x[b] = make_uint4(0u, 0u, 0u, 0u);
-            if (live[b]) {
-              const bf16* src = reinterpret_cast<const bf16*>(p.mc_base + p.data_off) + rs_stage_elem(p, rowv[b]) + colv[b];
-              x[b] = kb::multimem_ld_reduce_bf16x8(src);
-            }
+            if (v < total && col < p.N) x[b] = kb::multimem_ld_reduce_bf16x8(mc_stage + rs_stage_elem(p, row) + col);
           }
 #pragma unroll
-          for (int b = 0; b < 2; ++b) unpack8(x[b], accv[b]);
-        } else {
+          for (int b = 0; b < 8; ++b) {
+            const int v = v0 + b * 128;
+            const int row = r0 + v / VPR, col = c0 + (v % VPR) * 8;
+            if (v < total && col < p.N) {
+              float accv[8];
+              unpack8(x[b], accv);
+              finish(accv, row, col);
+            }
+          }
+        }
+      } else {
+        // Peer loads: two vectors per thread and up to eight sources in flight,
+        // summed in ascending rank order.
+        for (int v0 = rt; v0 < total; v0 += 2 * 128) {
+          float accv[2][8];
+          int rowv[2], colv[2];
+          bool live[2];
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            const int v = v0 + b * 128;
+            rowv[b] = r0 + v / VPR;
+            colv[b] = c0 + (v % VPR) * 8;
+            live[b] = v < total && colv[b] < p.N;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) accv[b][e] = 0.f;
+          }
 #pragma unroll 1
           for (int s0 = 0; s0 < p.world; s0 += 8) {
             uint4 x[2][8];
@@ -635,17 +654,10 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
               }
             }
           }
-        }
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
-          if (!live[b]) continue;
-          if (p.bias != nullptr) {
-            float bz[8];
-            unpack8(*reinterpret_cast<const uint4*>(p.bias + colv[b]), bz);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) accv[b][e] += p.bias_scale * bz[e];
+          for (int b = 0; b < 2; ++b) {
+            if (live[b]) finish(accv[b], rowv[b], colv[b]);
           }
-          *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(rowv[b] - row_begin) * p.N + colv[b]) = pack8(accv[b]);
         }
       }
     }
@@ -777,10 +789,13 @@ inline uint64_t round_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 struct EnvConfig {
   bool no_pair;
   bool timing;
+  bool tma_epilogue;
   int group_rows;
   EnvConfig() {
     const char* v = getenv("KB200_GEMM_NO_PAIR");
     no_pair = v != nullptr && v[0] == '1';
+    v = getenv("KB200_GEMM_EPILOGUE");  // "tma" (default) or "direct"
+    tma_epilogue = !(v != nullptr && v[0] == 'd');
     v = getenv("KB200_GEMM_TIMING");
     timing = v != nullptr && v[0] == '1';
     v = getenv("KB200_GEMM_GROUP_ROWS");
@@ -952,7 +967,8 @@ extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {
     if (rc != KB_OK) return rc;
     p.ag_own_direct = 1;
   }
-  if (p.mode != KB_GEMM_RS) {
+  const bool direct = p.mode == KB_GEMM_RS || !env.tma_epilogue;
+  if (!direct) {
     rc = make_tmap(&p.tmOut, a->out, a->M, a->N, OUT_BOX_COLS, OUT_BOX_ROWS);
     if (rc != KB_OK) return rc;
   }
@@ -961,17 +977,19 @@ extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {
   if (p.mode == KB_GEMM_PLAIN && grid > total_units) grid = total_units;  // the fused modes keep every CTA: their extra warps share the transfers
 
   const int threads = p.mode == KB_GEMM_PLAIN ? THREADS_BASE : THREADS_COMM;
-  const void* fns[2][3] = {
-      {(const void*)gemm_kernel<KB_GEMM_PLAIN, false>, (const void*)gemm_kernel<KB_GEMM_RS, false>,
-       (const void*)gemm_kernel<KB_GEMM_AG, false>},
-      {(const void*)gemm_kernel<KB_GEMM_PLAIN, true>, (const void*)gemm_kernel<KB_GEMM_RS, true>,
-       (const void*)gemm_kernel<KB_GEMM_AG, true>}};
-  const void* fn = fns[pair ? 1 : 0][p.mode];
+  const void* fns[2][2][3] = {
+      {{(const void*)gemm_kernel<KB_GEMM_PLAIN, false, false>, nullptr, (const void*)gemm_kernel<KB_GEMM_AG, false, false>},
+       {(const void*)gemm_kernel<KB_GEMM_PLAIN, false, true>, (const void*)gemm_kernel<KB_GEMM_RS, false, true>,
+        (const void*)gemm_kernel<KB_GEMM_AG, false, true>}},
+      {{(const void*)gemm_kernel<KB_GEMM_PLAIN, true, false>, nullptr, (const void*)gemm_kernel<KB_GEMM_AG, true, false>},
+       {(const void*)gemm_kernel<KB_GEMM_PLAIN, true, true>, (const void*)gemm_kernel<KB_GEMM_RS, true, true>,
+        (const void*)gemm_kernel<KB_GEMM_AG, true, true>}}};
+  const void* fn = fns[pair ? 1 : 0][direct ? 1 : 0][p.mode];
   {
-    static bool attr_set[64][2][3] = {};
-    if (dev < 0 || dev >= 64 || !attr_set[dev][pair ? 1 : 0][p.mode]) {
+    static bool attr_set[64][2][2][3] = {};
+    if (dev < 0 || dev >= 64 || !attr_set[dev][pair ? 1 : 0][direct ? 1 : 0][p.mode]) {
       KB_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      if (dev >= 0 && dev < 64) attr_set[dev][pair ? 1 : 0][p.mode] = true;
+      if (dev >= 0 && dev < 64) attr_set[dev][pair ? 1 : 0][direct ? 1 : 0][p.mode] = true;
     }
   }
   cudaLaunchConfig_t cfg = {};

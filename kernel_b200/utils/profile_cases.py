@@ -18,7 +18,7 @@ import os
 import torch
 
 
-def run_gemm(m: int, n: int, k: int, iters: int) -> None:
+def run_gemm(m: int, n: int, k: int, iters: int, pair=None) -> None:
     from ..ops.gemm import gemm
 
     dev = torch.device("cuda", 0)
@@ -31,7 +31,7 @@ def run_gemm(m: int, n: int, k: int, iters: int) -> None:
     for i in range(iters):
         if i == iters - 1:
             ev[0].record()
-        gemm(a, b, bias, out=out)
+        gemm(a, b, bias, out=out, pair=pair)
     ev[1].record()
     torch.cuda.synchronize()
     us = ev[0].elapsed_time(ev[1]) * 1e3
@@ -70,9 +70,10 @@ def main() -> None:
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=256)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--pair", type=int, default=None, help="gemm: 1 = CTA-pair kernel, 0 = single-CTA kernel, default: the faster of the two")
     ns = ap.parse_args()
     if ns.case == "gemm":
-        run_gemm(ns.m, ns.n, ns.k, ns.iters)
+        run_gemm(ns.m, ns.n, ns.k, ns.iters, None if ns.pair is None else bool(ns.pair))
     else:
         run_a2a(ns.tokens, ns.iters, fused=ns.case == "a2a")
 
