@@ -363,6 +363,27 @@ def run(args):
             dist.destroy_process_group()
             return 0
         raise
+    try:
+        return _measure(args, arm, rank, world, dev)
+    except BaseException:
+        # Leave in order even when something failed: wait for this rank's kernels and
+        # release the workspaces (which unbinds their memory from the multicast
+        # object) without waiting for peers that may be gone.
+        try:
+            torch.cuda.synchronize()
+            for mod in (getattr(arm, "a2a", None), getattr(arm, "rs", None), getattr(arm, "ag", None)):
+                for ctx in list(getattr(mod, "_contexts", {}).values()):
+                    for sub, _ in getattr(ctx, "_stream_state", {}).values():
+                        if sub is not ctx and sub.heap is not None:
+                            sub.heap.close(collective=False)
+                    if ctx.heap is not None:
+                        ctx.heap.close(collective=False)
+        except Exception:
+            pass
+        raise
+
+
+def _measure(args, arm, rank, world, dev):
     host, d = make_inputs(rank, world, dev)
     flush = L2Flush(dev)
     align = torch.zeros(1, device=dev)

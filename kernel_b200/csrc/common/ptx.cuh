@@ -62,6 +62,34 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return true;
 }
 
+// Cluster-scope acquire form of the bounded wait: for a barrier whose arrival
+// orders ordinary stores that a thread of ANOTHER CTA of the cluster made to this
+// CTA's shared memory (st.shared::cluster + mbarrier.arrive.release.cluster).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++spins & 0x3ffu) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
+  }
+  return true;
+}
+// 32-bit store into the shared memory of another CTA of the cluster (address from map_to_cta).
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
 // ----------------------------------------------------------------- TMA ----
 // 2-D tiled load global -> shared of one box, completion on an mbarrier.
 // Plain (single-CTA) form only.  x is the innermost coordinate and must keep
@@ -318,16 +346,19 @@ __device__ __forceinline__ void fence_gpu() { asm volatile("fence.acq_rel.gpu;" 
 // away from the very stores it is waiting for.  A single poller of a line passes
 // 0 and spins without pausing (a pause costs about a microsecond of reaction
 // time).  `sys` false: the word is written by this GPU only, device scope is
-// enough for the polls and the fence.
+// enough for the polls and the fence.  `acquire_loads`: poll with ld.acquire.sys
+// and skip the fence; for a lone poller that is cheaper than relaxed polls plus
+// fence.acq_rel.sys, which also waits for the acknowledgements of every store this
+// GPU has in flight to its peers (several microseconds on an NVSwitch system).
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint64_t limit_ns,
-                                             uint32_t max_pause_ns = 512, bool sys = true) {
+                                             uint32_t max_pause_ns = 512, bool sys = true, bool acquire_loads = false) {
   auto poll = [&]() -> bool {
-    const uint32_t v = sys ? ld_relaxed_sys_u32(flag) : ld_relaxed_gpu_u32(flag);
+    const uint32_t v = !sys ? ld_relaxed_gpu_u32(flag) : (acquire_loads ? ld_acquire_sys_u32(flag) : ld_relaxed_sys_u32(flag));
     return static_cast<int32_t>(v - want) >= 0;
   };
   auto acquire = [&]() {
-    if (sys) fence_sys();
-    else fence_gpu();
+    if (!sys) fence_gpu();
+    else if (!acquire_loads) fence_sys();
   };
   if (poll()) {
     acquire();

@@ -88,28 +88,27 @@ __device__ __forceinline__ void fence_for(const A2aParams& p) {
   else kb::fence_sys();
 }
 
-// Publishes this rank's flag of phase `which` on rank `dst` (one thread per destination).
-__device__ __forceinline__ void post_flag(const A2aParams& p, int dst, int which) {
-  if (p.world == 1) kb::st_release_gpu_u32(flag_ptr(p, dst, which, p.rank), p.epoch);
-  else kb::st_release_sys_u32(flag_ptr(p, dst, which, p.rank), p.epoch);
-}
-
-// Last-block-done: returns true in exactly one CTA (the last to arrive) once
-// the writes of all CTAs are ordered before it.
-__device__ __forceinline__ bool last_block_done(const A2aParams& p, uint32_t* counter, uint32_t total) {
-  __shared__ uint32_t s_last;
+// Counts this CTA as done with a phase (its writes ordered before the count) and,
+// in the one CTA that arrives last, publishes this rank's flag of phase `which` on
+// every rank.  One thread does the fence after the count and all the flag stores:
+// fence + relaxed stores by the same thread is a release, and the critical path
+// holds one system-scope fence here instead of one per posting thread.
+__device__ __forceinline__ void finish_phase(const A2aParams& p, uint32_t* counter, uint32_t total, int which) {
   __syncthreads();
   if (threadIdx.x == 0) {
     fence_for(p);
     const uint32_t old = atomicAdd(counter, 1u);
-    s_last = (old == total - 1u) ? 1u : 0u;
-    if (s_last) {
+    if (old == total - 1u) {
       *counter = 0u;  // ready for the next launch
       fence_for(p);
+      for (int dst = 0; dst < p.world; ++dst) {
+        uint32_t* f = flag_ptr(p, dst, which, p.rank);
+        if (p.world == 1) kb::st_release_gpu_u32(f, p.epoch);
+        else kb::st_relaxed_sys_u32(f, p.epoch);
+      }
     }
   }
   __syncthreads();
-  return s_last != 0u;
 }
 
 // Waits until source `src` has reached phase `which` of this epoch.  In a fused
@@ -133,7 +132,7 @@ __device__ __forceinline__ void poller_body(const A2aParams& p) {
   const int s = threadIdx.x;
   if (s >= p.world) return;
   for (int which = 0; which < 2; ++which) {
-    if (!kb::wait_flag_ge(flag_ptr(p, p.rank, which, s), p.epoch, p.limit_ns, 0, p.world > 1)) {
+    if (!kb::wait_flag_ge(flag_ptr(p, p.rank, which, s), p.epoch, p.limit_ns, 0, p.world > 1, true)) {
       kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_POLLER, (uint32_t)(which * KB_MAX_WORLD + s), p.epoch);
     }
     kb::st_release_gpu_u32(go_ptr(p, which, s), p.epoch);
@@ -291,9 +290,7 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh, i
     }
   }
   uint32_t* sync = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.sync_off);
-  if (last_block_done(p, &sync[0], nworkers)) {
-    if (tid < p.world) post_flag(p, tid, 0);  // every posting thread releases for itself
-  }
+  finish_phase(p, &sync[0], nworkers, 0);
   stamp(p, ST_DISPATCH_FLAG);
 }
 
@@ -358,30 +355,65 @@ struct Vec16<float> {
   }
 };
 
-// The simulated expert, source by source in arrival order of a ring that starts
-// at this rank (whose own rows are there first): a source's rows are scaled as
-// soon as that source's dispatch flag is seen, while later sources may still be
-// sending.  Rows of one source are dealt round-robin to the data CTAs, starting
-// at a CTA that depends on the source so that remainders spread out.
+// Non-blocking form of wait_arrival: true if source `src` has reached phase `which`.
+template <bool kFused>
+__device__ __forceinline__ bool has_arrived(const A2aParams& p, int which, int src) {
+  const bool sys = !kFused && p.world > 1;
+  const uint32_t* word = kFused ? go_ptr(p, which, src) : flag_ptr(p, p.rank, which, src);
+  const uint32_t v = sys ? kb::ld_relaxed_sys_u32(word) : kb::ld_relaxed_gpu_u32(word);
+  if (static_cast<int32_t>(v - p.epoch) < 0) return false;
+  if (sys) kb::fence_sys();
+  else kb::fence_gpu();
+  return true;
+}
+
+// The simulated expert, in rounds.  A round waits for the next missing source in
+// ring order (starting with this rank, whose own rows are there first), takes
+// along every other source whose dispatch flag has arrived meanwhile, and scales
+// the rows of all of them in one batch: the counts of the batch's sources are
+// scanned by different warps at the same time, and the CTA's rows of the whole
+// batch form one list that is worked two rows per step (eight 16-byte loads per
+// thread in flight).  When the ranks run aligned this is one round or two; when a
+// source is late, everything that has arrived is done before the wait for it.
+// Rows of a source are dealt round-robin to the data CTAs, starting at a CTA
+// that depends on the source so that remainders spread out.
 template <typename T, bool kFused>
 __device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh, int nworkers) {
-  int32_t* incl = sh;  // [El] inclusive prefix of the current source's counts
+  int32_t* incl = sh;  // [world][El] clamped inclusive prefix of each source's counts
+  __shared__ uint32_t s_batch;
+  __shared__ int32_t s_n[KB_MAX_WORLD], s_first[KB_MAX_WORLD];
   const int tid = threadIdx.x;
   const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const uint32_t all = p.world >= 32 ? 0xffffffffu : ((1u << p.world) - 1u);
+  uint32_t done = 0;
   uint64_t waited = 0;
-  for (int si = 0; si < p.world; ++si) {
-    const int s = (p.rank + si) % p.world;
+  bool first_round = true;
+  while (done != all) {
     if (tid == 0) {
+      int s = p.rank;
+      for (int si = 0; si < p.world; ++si) {
+        s = (p.rank + si) % p.world;
+        if (!((done >> s) & 1u)) break;
+      }
       const uint64_t w0 = (p.trace != nullptr && blockIdx.x == 0) ? kb::globaltimer_ns() : 0;
       if (!wait_arrival<kFused>(p, 0, s)) {
         kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_EXP_FLAG, (uint32_t)s, p.epoch);
       }
       if (p.trace != nullptr && blockIdx.x == 0) waited += kb::globaltimer_ns() - w0;
+      s_batch = 1u << s;
     }
     __syncthreads();
-    if (si == 0) stamp(p, ST_EXPERT_GO);
-    // Counts of this source -> clamped inclusive prefix, by one warp.
-    if (tid < 32) {
+    if (tid < p.world && !((done >> tid) & 1u) && !((s_batch >> tid) & 1u)) {
+      if (has_arrived<kFused>(p, 0, tid)) atomicOr(&s_batch, 1u << tid);
+    }
+    __syncthreads();
+    const uint32_t batch = s_batch & ~done;
+    if (first_round) stamp(p, ST_EXPERT_GO);
+    first_round = false;
+    // Counts of the batch's sources -> clamped inclusive prefixes, one warp per source.
+    for (int s = warp; s < p.world; s += A2A_THREADS / 32) {
+      if (!((batch >> s) & 1u)) continue;
       const int32_t* counts = counts_ptr(p, p.rank, s);
       int carry = 0;
       for (int base = 0; base < p.El; base += 32) {
@@ -396,28 +428,50 @@ __device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh, int
         }
         v += carry;
         if (v > p.cap) v = p.cap;
-        if (le < p.El) incl[le] = v;
+        if (le < p.El) incl[s * p.El + le] = v;
         carry = __shfl_sync(0xffffffffu, v, 31);
       }
     }
     __syncthreads();
-    const int rows = incl[p.El - 1];
-    const int first = static_cast<int>((blockIdx.x + 37u * static_cast<unsigned>(s)) % static_cast<unsigned>(nworkers));
-    // Two rows of this CTA per step: up to eight 16-byte loads per thread in flight.
-    for (int rowA = first; rowA < rows; rowA += 2 * nworkers) {
-      int rowv[2] = {rowA, rowA + nworkers};
+    if (tid < p.world) {
+      int n = 0, first = 0;
+      if ((batch >> tid) & 1u) {
+        const int rows = incl[tid * p.El + p.El - 1];
+        first = static_cast<int>((blockIdx.x + 37u * static_cast<unsigned>(tid)) % static_cast<unsigned>(nworkers));
+        n = rows > first ? (rows - first + nworkers - 1) / nworkers : 0;
+      }
+      s_n[tid] = n;
+      s_first[tid] = first;
+    }
+    __syncthreads();
+    int n_tot = 0;
+    for (int s = 0; s < p.world; ++s) n_tot += s_n[s];
+    // Entry j of this CTA's list -> (source, row): the sources' shares are laid end to end.
+    auto entry = [&](int j, int& src_rank, int& row) {
+      int s = 0;
+      while (j >= s_n[s]) {
+        j -= s_n[s];
+        ++s;
+      }
+      src_rank = s;
+      row = s_first[s] + j * nworkers;
+    };
+    for (int j0 = 0; j0 < n_tot; j0 += 2) {
+      bool have[2];
       float scale[2];
       const uint4* src[2];
       uint4* dst[2];
 #pragma unroll
       for (int b = 0; b < 2; ++b) {
-        if (rowv[b] >= rows) rowv[b] = -1;
-        const int row = rowv[b] < 0 ? rowA : rowv[b];
+        have[b] = j0 + b < n_tot;
+        int s = 0, row = 0;
+        entry(have[b] ? j0 + b : j0, s, row);
         // first local expert whose inclusive prefix exceeds row
+        const int32_t* in = incl + s * p.El;
         int lo = 0, hi = p.El - 1;
         while (lo < hi) {
           const int mid = (lo + hi) >> 1;
-          if (incl[mid] > row) hi = mid; else lo = mid + 1;
+          if (in[mid] > row) hi = mid; else lo = mid + 1;
         }
         scale[b] = 1.0f;
         if (p.scale_mode == 1) scale[b] = static_cast<float>(1 + p.rank);
@@ -432,7 +486,7 @@ __device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh, int
 #pragma unroll
           for (int u = 0; u < 4; ++u) {  // all loads of this thread first: one latency per pair of rows
             const int v = vb + u * blockDim.x;
-            if (rowv[b] >= 0 && v < p.vecs) in[b][u] = kb::ld_sys_v4(src[b] + v);
+            if (have[b] && v < p.vecs) in[b][u] = kb::ld_sys_v4(src[b] + v);
           }
         }
 #pragma unroll
@@ -440,7 +494,7 @@ __device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh, int
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int v = vb + u * blockDim.x;
-            if (rowv[b] >= 0 && v < p.vecs) {
+            if (have[b] && v < p.vecs) {
               float f[Vec16<T>::N];
               Vec16<T>::load(in[b][u], f);
 #pragma unroll
@@ -451,14 +505,13 @@ __device__ __forceinline__ void expert_body(const A2aParams& p, int32_t* sh, int
         }
       }
     }
-    __syncthreads();  // incl is rewritten for the next source
+    done |= batch;
+    __syncthreads();  // s_batch, s_n and the prefixes are rewritten by the next round
   }
   if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) p.trace[ST_WAITED_EXPERT] = waited;
   stamp(p, ST_EXPERT_ROWS);
   uint32_t* sync = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.sync_off);
-  if (last_block_done(p, &sync[1], nworkers)) {
-    if (tid < p.world) post_flag(p, tid, 1);
-  }
+  finish_phase(p, &sync[1], nworkers, 1);
   stamp(p, ST_EXPERT_FLAG);
 }
 
@@ -565,7 +618,7 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_fused_kernel(const A2aParams 
   }
   dispatch_body(p, sh, nworkers);
   __syncthreads();
-  expert_body<T, true>(p, sh, nworkers);  // uses the first experts-per-rank words only: the entry tables stay intact
+  expert_body<T, true>(p, sh, nworkers);  // uses the first E words only: the entry tables behind them stay intact
   __syncthreads();
   combine_body<T, true>(p, sh + 3 * p.E, sh + 3 * p.E + MAX_ENT_PER_CTA);
 }
@@ -744,7 +797,7 @@ extern "C" int kb_a2a_expert_scale(const KbA2aArgs* a, void* stream) {
   A2aParams p;
   rc = fill_params(a, &p, sms);
   if (rc != KB_OK) return rc;
-  const size_t smem = p.El * sizeof(int32_t);
+  const size_t smem = p.E * sizeof(int32_t);
   const int grid = a->num_ctas > 0 ? a->num_ctas : 2 * sms;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (a->dtype) {
@@ -780,7 +833,7 @@ extern "C" int kb_a2a_combine(const KbA2aArgs* a, void* stream) {
 template <typename T>
 static int launch_fused(const A2aParams& p, int sms, cudaStream_t st) {
   const size_t smem_d = (3 * p.E + 2 * MAX_ENT_PER_CTA) * sizeof(int32_t);
-  const size_t smem_e = p.El * sizeof(int32_t);
+  const size_t smem_e = p.E * sizeof(int32_t);
   const size_t smem = smem_d > smem_e ? smem_d : smem_e;
   // The occupancy query costs microseconds of host time; its answer depends only
   // on the kernel instance and the shared-memory size.

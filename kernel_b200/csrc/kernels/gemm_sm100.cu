@@ -78,6 +78,8 @@ constexpr int BAR_BYTES = 256;
 constexpr int SMEM_BYTES = 1024 + 7 * 32768 + BAR_BYTES;  // 6 pair stages + staging = 4 single stages + staging = 7 pair stages
 constexpr int THREADS_BASE = 256;             // warps 0..3 control, 4..7 epilogue
 constexpr int THREADS_COMM = 384;             // + warps 8..11: all-gather pushers or reduce-scatter reducers
+constexpr int SCHED_RING = 4;                 // AG: claimed tile positions in flight between the claimer and the other roles
+constexpr int AG_TILE_CLAIM = 128;            // AG: two words of the counter block (one per epoch parity) that hand out tile positions
 constexpr int RS_ROW_GROUP = 64;              // rows of one reduction unit
 constexpr int RS_UNIT_COLS = 128;             // columns of one reduction unit
 
@@ -116,6 +118,7 @@ enum Site : uint32_t {
   SITE_EPI_TFULL = 4,
   SITE_RS_FLAG = 5,
   SITE_AG_FLAG = 6,
+  SITE_SCHED = 7,
 };
 
 struct Smem {
@@ -128,6 +131,9 @@ struct Smem {
   uint64_t* tempty;
   uint32_t* tmem_slot;
   volatile uint32_t* abort;
+  uint64_t* sfull;              // AG: a claimed position is in sched_pos[slot]
+  uint64_t* sempty;             // AG: every role has read sched_pos[slot] (on the leader CTA)
+  volatile int32_t* sched_pos;  // AG: ring of claimed schedule positions, -1 = no more tiles
 };
 
 template <bool kPair, bool kDirect>
@@ -145,6 +151,10 @@ __device__ __forceinline__ Smem carve(uint8_t* raw) {
   s.tempty = bars + 2 * MAX_STAGES + 2;
   s.tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 4);
   s.abort = s.tmem_slot + 1;
+  s.sfull = bars + 2 * MAX_STAGES + 5;
+  s.sempty = s.sfull + SCHED_RING;
+  s.sched_pos = reinterpret_cast<volatile int32_t*>(s.sempty + SCHED_RING);
+  static_assert((2 * MAX_STAGES + 5 + 2 * SCHED_RING) * 8 + SCHED_RING * 4 <= BAR_BYTES, "barrier block too small");
   return s;
 }
 
@@ -161,6 +171,12 @@ __device__ __forceinline__ Smem carve(uint8_t* raw) {
 //   AG     this rank's own blocks (no transfer needed), then block c of every
 //          other source (nearest first) for c = 0, 1, ...: the order in which
 //          the pushes arrive.
+//
+// PLAIN and RS walk the sequence statically (CTA or CTA pair i takes positions
+// i, i + n, ...).  AG hands positions out from a counter: a CTA pair whose next
+// tile waits for rows that have not arrived simply ends up with fewer tiles,
+// instead of finishing late with its fixed share (with a static walk the pairs
+// that start on remote rows lose the whole arrival time of the first blocks).
 __host__ __device__ __forceinline__ void tile_at(const GemmParams& p, int pos, int& mbq, int& nb) {
   const int GROUP_M = p.group;
   const int per_group = GROUP_M * p.NB;
@@ -313,6 +329,12 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       kb::mbar_init(&sm.tfull[a], 1);
       kb::mbar_init(&sm.tempty[a], kPair ? 8 : 4);  // epilogue warps of both CTAs release the leader's accumulator
     }
+    if (kAG) {
+      for (int r = 0; r < SCHED_RING; ++r) {
+        kb::mbar_init(&sm.sfull[r], 1);
+        kb::mbar_init(&sm.sempty[r], kPair ? 10 : 5);  // MMA issuer, epilogue warps of both CTAs, the partner's producer
+      }
+    }
     *sm.abort = 0;
     kb::mbar_fence_init();
   }
@@ -324,6 +346,9 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       kb::tmem_alloc(sm.tmem_slot, TMEM_COLS);
       kb::tmem_relinquish();
     }
+  }
+  if (kAG && blockIdx.x == 0 && tid == 32) {
+    reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.counter_off)[AG_TILE_CLAIM + ((p.epoch & 1u) ^ 1u)] = 0u;
   }
   if (warp == 0 && lane == 0) {
     kb::tma_prefetch_desc(&p.tmA);
@@ -337,6 +362,47 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
   kb::tc_fence_after_sync();
   const uint32_t tmem_base = *sm.tmem_slot;
 
+  // ---- AG: dynamic tile positions -------------------------------------------
+  // The leader's producer thread claims the next position from a counter in this
+  // rank's counter block and publishes it in a ring slot of both CTAs; every other
+  // role reads it from its own CTA's slot and acknowledges on the leader's
+  // barrier.  Calls alternate between two counters by epoch parity; a call zeroes
+  // the counter of the other parity, which nobody uses while it runs, so the
+  // counters are right whatever happened to the call before.
+  auto claim_tile = [&](uint32_t iter) -> int {
+    const int slot = static_cast<int>(iter % SCHED_RING);
+    if (iter >= SCHED_RING && !kb::mbar_wait_bounded(&sm.sempty[slot], ((iter / SCHED_RING) - 1u) & 1u, p.limit_ns)) {
+      kb::report_status(p.status, KB_DEV_TIMEOUT_MBAR, SITE_SCHED, iter, p.epoch);
+      *sm.abort = 1;
+      return -1;
+    }
+    uint32_t* counter = reinterpret_cast<uint32_t*>(p.peer_base[p.rank] + p.counter_off) + AG_TILE_CLAIM + (p.epoch & 1u);
+    const uint32_t v = atomicAdd(counter, 1u);
+    const int pos = v < static_cast<uint32_t>(total_tiles) ? static_cast<int>(v) : -1;
+    sm.sched_pos[slot] = pos;
+    if constexpr (kPair) {
+      kb::st_shared_cluster_u32(kb::map_to_cta(kb::smem_u32(const_cast<int32_t*>(&sm.sched_pos[slot])), 1u), static_cast<uint32_t>(pos));
+      kb::mbar_arrive_cluster(kb::map_to_cta(kb::smem_u32(&sm.sfull[slot]), 1u));
+    }
+    kb::mbar_arrive(&sm.sfull[slot]);
+    return pos;
+  };
+  auto read_tile = [&](uint32_t iter) -> int {
+    const int slot = static_cast<int>(iter % SCHED_RING);
+    const uint32_t parity = (iter / SCHED_RING) & 1u;
+    const bool ok = (kPair && !leader) ? kb::mbar_wait_bounded_cluster(&sm.sfull[slot], parity, p.limit_ns)
+                                       : kb::mbar_wait_bounded(&sm.sfull[slot], parity, p.limit_ns);
+    if (!ok) {
+      kb::report_status(p.status, KB_DEV_TIMEOUT_MBAR, SITE_SCHED, iter, p.epoch);
+      *sm.abort = 1;
+      return -1;
+    }
+    const int pos = sm.sched_pos[slot];
+    if (kPair && !leader) kb::mbar_arrive_cluster(kb::map_to_cta(kb::smem_u32(&sm.sempty[slot]), 0u));
+    else kb::mbar_arrive(&sm.sempty[slot]);
+    return pos;
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer ----
     if (lane == 0) {
@@ -345,7 +411,15 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       uint64_t ready_mask[4] = {0ull, 0ull, 0ull, 0ull};  // row blocks already seen complete
       uint64_t waited_ns = 0;
       bool ok = true;
-      for (int pos = sched_id; pos < total_tiles && ok; pos += sched_n) {
+      for (uint32_t iter = 0; ok; ++iter) {
+        int pos;
+        if constexpr (kAG) {
+          pos = leader ? claim_tile(iter) : read_tile(iter);
+          if (pos < 0) break;
+        } else {
+          pos = sched_id + static_cast<int>(iter) * sched_n;
+          if (pos >= total_tiles) break;
+        }
         int mbq, nb;
         tile_at(p, pos, mbq, nb);
         const int mb = kPair ? 2 * mbq + static_cast<int>(cta_rank) : mbq;
@@ -359,7 +433,9 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           const int s_hi = last_row / p.rpo;
           const uint64_t w0 = p.timing ? kb::globaltimer_ns() : 0;
           for (int src = s_lo; src <= s_hi; ++src) {
-            if (!kb::wait_flag_ge(ag_flag(p, p.rank, src, mb), p.epoch, p.limit_ns)) {
+            // acquire loads, no system-scope fence: that fence would wait for the acknowledgements of
+            // the pushes this GPU has in flight, microseconds per row block on the producer's path
+            if (!kb::wait_flag_ge(ag_flag(p, p.rank, src, mb), p.epoch, p.limit_ns, 512, true, true)) {
               kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_AG_FLAG, (uint32_t)src, p.epoch);
             }
           }
@@ -403,7 +479,15 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t ph = 0;
       uint32_t it = 0;
       bool ok = true;
-      for (int pos = sched_id; pos < total_tiles && ok; pos += sched_n, ++it) {
+      for (;; ++it) {
+        int pos;
+        if constexpr (kAG) {
+          pos = read_tile(it);
+        } else {
+          pos = sched_id + static_cast<int>(it) * sched_n;
+          if (pos >= total_tiles) pos = -1;
+        }
+        if (pos < 0 || !ok) break;
         const uint32_t acc = it & 1u;
         const uint32_t aph = (it >> 1) & 1u;
         if (!kb::mbar_wait_bounded(&sm.tempty[acc], aph ^ 1u, p.limit_ns)) {
@@ -478,7 +562,17 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
         }
       }
     };
-    for (int pos = sched_id; pos < total_tiles; pos += sched_n, ++it) {
+    for (;; ++it) {
+      int pos;
+      if constexpr (kAG) {
+        pos = 0;
+        if (lane == 0) pos = read_tile(it);
+        pos = __shfl_sync(0xffffffffu, pos, 0);
+      } else {
+        pos = sched_id + static_cast<int>(it) * sched_n;
+        if (pos >= total_tiles) pos = -1;
+      }
+      if (pos < 0) break;
       int mbq, nb;
       tile_at(p, pos, mbq, nb);
       const int mb = kPair ? 2 * mbq + static_cast<int>(cta_rank) : mbq;
@@ -570,7 +664,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       const int tile_id = (r0 / BM) * p.NB + nb;
       if (rt < p.world) {
         const uint64_t w0 = p.timing ? kb::globaltimer_ns() : 0;
-        if (!kb::wait_flag_ge(rs_flag(p, p.rank, rt, tile_id), p.epoch, p.limit_ns, 256)) {
+        if (!kb::wait_flag_ge(rs_flag(p, p.rank, rt, tile_id), p.epoch, p.limit_ns, 256, true, true)) {
           kb::report_status(p.status, KB_DEV_TIMEOUT_FLAG, SITE_RS_FLAG, (uint32_t)rt, p.epoch);
         }
         if (p.timing) waited_ns += kb::globaltimer_ns() - w0;
@@ -861,7 +955,7 @@ extern "C" uint64_t kb_gemm_ag_flag_bytes(int M, int world) {
 extern "C" uint64_t kb_gemm_ag_counter_bytes(int M, int world) {
   (void)M;
   (void)world;
-  return 1024;  // 64 completion counters and 64 claim counters (at most eight groups are used)
+  return 1024;  // words 0..63 completion counters and 64..127 slice-claim counters of the pushes (at most eight groups are used), 128..129 tile-claim counters
 }
 
 extern "C" int kb_gemm(const KbGemmArgs* a, void* stream_v) {

@@ -73,7 +73,8 @@ class MoEAllToAll:
             counts = (self.world * self.El * 4 + 255) // 256 * 256
             flag_bytes, sync_bytes = int(lib.kb_a2a_flag_bytes()), int(lib.kb_a2a_sync_bytes())
             need = 2 * rows + counts + flag_bytes + sync_bytes + 4096
-            self.heap = heap or (SymmHeap(need, group=group, device=device) if self.native
+            # no multicast mapping here: these kernels use peer loads and stores only
+            self.heap = heap or (SymmHeap(need, group=group, device=device, nvls=False) if self.native
                                  else SymmHeap(need, group=group, backend="host", timeout_s=_WAIT_LIMIT_NS / 1e9 + 5))
             self.recv_off = self.heap.alloc(rows)
             self.y_off = self.heap.alloc(rows)

@@ -89,8 +89,8 @@ class SymmHeap:
         self.backend = backend
         self.nbytes = int(self._lib.kb_symm_segment_bytes(self._h))
         self._map(session)
-        if nvls is None:
-            nvls = os.environ.get("KB200_NVLS", "0") == "1"
+        if nvls is None:  # KB200_NVLS=0 keeps every kernel on plain peer loads and stores
+            nvls = os.environ.get("KB200_NVLS", "1") == "1"
         if nvls and backend == "vmm" and self.world > 1:
             self._setup_multicast(session)
         self._control_barrier()

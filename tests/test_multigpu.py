@@ -205,9 +205,15 @@ def _fused_gemms_over_nvls(rank, world):
     return res
 
 
-def test_fused_gemms_over_nvls():
+@pytest.mark.parametrize("nvls", ["1", "0"])
+def test_fused_gemms_with_and_without_nvls(nvls):
     world = _world()
-    res = run_ranks(_fused_gemms_over_nvls, world, backend="nccl", timeout=300, env={"KB200_NVLS": "1"})
+    res = run_ranks(_fused_gemms_over_nvls, world, backend="nccl", timeout=300, env={"KB200_NVLS": nvls})
+    if nvls == "0":
+        for per_rank in res:
+            for op, mc, ok, msg in per_rank:
+                assert not mc and ok, (op, msg)
+        return
     if not any(mc for per_rank in res for _, mc, _, _ in per_rank):
         pytest.skip("the devices or the driver offer no multicast objects")
     for per_rank in res:
@@ -369,5 +375,6 @@ def _rank_leaves(rank, world):
 
 def test_departed_rank_is_seen_on_the_host_before_the_next_launch(monkeypatch):
     world = 2
-    res = run_ranks(_rank_leaves, world, backend="nccl", timeout=120, env={"NCCL_NVLS_ENABLE": "0"})
+    # no multicast anywhere in a test where a rank stops taking part: neither in NCCL nor in the heap
+    res = run_ranks(_rank_leaves, world, backend="nccl", timeout=120, env={"NCCL_NVLS_ENABLE": "0", "KB200_NVLS": "0"})
     assert all(gone == [world - 1] for gone in res)

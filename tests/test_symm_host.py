@@ -162,6 +162,44 @@ def test_moe_wait_names_the_rank_that_never_arrived():
     assert "rank 1 never finished its dispatch of epoch 2" in res[0]
 
 
+def _moe_recovers_after_a_late_rank(rank, world):
+    """Rank 1 sits out one call, so rank 0's wait runs out; both then call
+    ``recover()`` (rank 1 is one call behind: the ranks agree on the largest call
+    number) and the next round trip is right on both."""
+    import time
+
+    import torch
+    import torch.distributed as dist
+
+    from kernel_b200.ops.dispatch_combine import MoEAllToAll
+
+    ctx = MoEAllToAll(8, 2, 32, 4, dtype=torch.float32, device="cpu")
+    g = torch.Generator().manual_seed(rank)
+    x = torch.randn(4, 32, generator=g)
+    idx = torch.tensor([[0, 5], [1, 4], [2, 7], [3, 6]], dtype=torch.int32)
+    w = torch.full((4, 2), 0.5)
+    first = ctx.dispatch_scale_combine(x, idx, w)
+    timed_out = False
+    if rank == 0:
+        try:
+            ctx.dispatch_scale_combine(x, idx, w)
+        except N.SymmTimeoutError:
+            timed_out = True
+    else:
+        time.sleep(0.8)  # longer than the wait limit: rank 0 gives up meanwhile
+    dist.barrier()
+    ctx.recover()
+    again = ctx.dispatch_scale_combine(x, idx, w)
+    ok = bool(torch.allclose(again, first)) and bool(torch.allclose(again, x))  # weights sum to one, identity expert
+    ctx.heap.close()
+    return timed_out, ok
+
+
+def test_moe_context_recovers_after_a_wait_ran_out():
+    res = run_ranks(_moe_recovers_after_a_late_rank, 2, env={"KB200_WAIT_LIMIT_MS": "300"})
+    assert res[0] == (True, True) and res[1] == (False, True)
+
+
 def test_multicast_probe_and_entry_points_fail_cleanly_without_a_device():
     """No driver, no multicast: the probe says no and the set-up entry points refuse
     a heap that is not a VMM heap, instead of touching the driver."""
