@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <stdlib.h>
 
 #include "../common/host_util.h"
 #include "../common/ptx.cuh"
@@ -33,6 +34,11 @@ namespace {
 constexpr int A2A_THREADS = 256;
 constexpr int MAX_EXPERTS = 1024;
 constexpr int MAX_ENT_PER_CTA = 2048;
+// Dispatch push through the bulk-copy engine: a slice of a token row is brought
+// into one of two shared-memory buffers with one cp.async.bulk and sent to its k
+// destinations with one cp.async.bulk each.
+constexpr int ROWBUF_BYTES = 16384;
+constexpr int BULK_MIN_BYTES = 1024;  // shorter slices go the load / store way
 // Every (phase, source) flag sits on a 128-byte line of its own: a peer's flag
 // store never queues behind polls of another source's flag.
 constexpr int FLAG_STRIDE_WORDS = 32;
@@ -56,6 +62,7 @@ struct A2aParams {
   uint32_t* status;
   uint64_t limit_ns;
   uint64_t* trace;
+  int bulk_min_bytes;  // row slices at least this long are pushed by the bulk-copy engine; 0x7fffffff: never
 };
 
 // Phase stamps (nanoseconds of the global timer) written by thread 0 of CTA 0.
@@ -191,6 +198,14 @@ __device__ __forceinline__ void expert_offsets(const int32_t* tot, int32_t* off,
 }
 
 __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh, int nworkers) {
+  // behind the tables: two row buffers (128-byte aligned) and their two mbarriers
+  uint8_t* rowbuf = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sh + 3 * p.E + 2 * MAX_ENT_PER_CTA) + 127) & ~uintptr_t(127));
+  uint64_t* rowbar = reinterpret_cast<uint64_t*>(rowbuf + 2 * ROWBUF_BYTES);
+  if (threadIdx.x == 0) {
+    kb::mbar_init(&rowbar[0], 1);
+    kb::mbar_init(&rowbar[1], 1);
+    kb::mbar_fence_init();
+  }
   int32_t* tot = sh;               // [E] entries per expert, whole rank
   int32_t* pre = tot + p.E;        // [E] entries per expert before this CTA's tokens
   int32_t* off = pre + p.E;        // [E] first slot of the expert inside its owner's region
@@ -256,6 +271,51 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh, i
   __syncthreads();
   stamp(p, ST_SLOTS);
 
+  const int slice_bytes = (v1 - v0) * 16;
+  if (slice_bytes >= p.bulk_min_bytes) {
+    // Payload through the bulk-copy engine, driven by one thread: piece n of the
+    // CTA's rows (at most ROWBUF_BYTES of one token row) is loaded into buffer
+    // n & 1 while the k stores of piece n - 1 are still leaving the other buffer.
+    // The stores go to peer memory as large packets and cost the SM no issue
+    // slots; their completion (wait_group 0) precedes this CTA's count below.
+    if (tid == 0) {
+      const int pieces_per_row = (slice_bytes + ROWBUF_BYTES - 1) / ROWBUF_BYTES;
+      const int n_pieces = (t1 - t0) * pieces_per_row;
+      auto piece = [&](int n, int& t, int& off, int& bytes) {
+        t = t0 + n / pieces_per_row;
+        off = v0 * 16 + (n % pieces_per_row) * ROWBUF_BYTES;
+        bytes = min(ROWBUF_BYTES, v0 * 16 + slice_bytes - off);
+      };
+      auto load = [&](int n) {
+        int t, off, bytes;
+        piece(n, t, off, bytes);
+        kb::mbar_arrive_expect_tx(&rowbar[n & 1], static_cast<uint32_t>(bytes));
+        kb::bulk_load(rowbuf + (n & 1) * ROWBUF_BYTES, p.x + static_cast<size_t>(t) * p.row_bytes + off, bytes, &rowbar[n & 1]);
+      };
+      if (n_pieces > 0) load(0);
+      for (int n = 0; n < n_pieces; ++n) {
+        if (n + 1 < n_pieces) {
+          if (n >= 1) kb::bulk_wait_group_read<0>();  // the stores of piece n - 1 have read the buffer piece n + 1 goes into
+          load(n + 1);
+        }
+        if (!kb::mbar_wait_bounded(&rowbar[n & 1], (n >> 1) & 1u, p.limit_ns)) {
+          kb::report_status(p.status, KB_DEV_TIMEOUT_MBAR, SITE_DISP_IDX, (uint32_t)n, p.epoch);
+          break;
+        }
+        int t, off, bytes;
+        piece(n, t, off, bytes);
+        for (int kk = 0; kk < p.k; ++kk) {
+          const int i = (t - t0) * p.k + kk;
+          const int slot = ent_slot[i];
+          if (slot < 0) continue;
+          kb::bulk_store(rows_ptr(p, ent_e[i] / p.El, p.recv_off, p.rank, slot) + off, rowbuf + (n & 1) * ROWBUF_BYTES, bytes);
+        }
+        kb::bulk_commit_group();
+      }
+      kb::bulk_wait_group<0>();          // every store has been performed
+      kb::fence_proxy_async_global();    // and is ordered before the ordinary accesses that follow (the count, the flag)
+    }
+  } else {
   // Payload: every 16-byte vector is read once and stored k times.  A thread
   // first issues all the loads of its (up to four) vectors of a row, so that the
   // load latency is paid once per row, not once per vector.
@@ -281,6 +341,7 @@ __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh, i
         }
       }
     }
+  }
   }
   stamp(p, ST_PUSHED);
   // Per-(source, expert) counts for every destination.
@@ -661,6 +722,12 @@ __global__ void post_ready_kernel(const A2aParams p) {
   }
 }
 
+// Dynamic shared memory of a kernel that runs the dispatch phase: the five tables,
+// alignment slack, two row buffers, two mbarriers.
+size_t dispatch_smem_bytes(int experts) {
+  return (3 * static_cast<size_t>(experts) + 2 * MAX_ENT_PER_CTA) * sizeof(int32_t) + 128 + 2 * ROWBUF_BYTES + 16;
+}
+
 int fill_params(const KbA2aArgs* a, A2aParams* p, int sms) {
   if (a == nullptr) return KB_ERR_ARG;
   if (a->world < 1 || a->world > KB_MAX_WORLD || a->rank < 0 || a->rank >= a->world) {
@@ -720,6 +787,13 @@ int fill_params(const KbA2aArgs* a, A2aParams* p, int sms) {
   p->status = a->status;
   p->limit_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
   p->trace = a->trace;
+  {
+    static const int bulk_min = [] {
+      const char* v = getenv("KB200_A2A_BULK");  // 0: ordinary loads and stores only
+      return (v != nullptr && v[0] == '0') ? 0x7fffffff : BULK_MIN_BYTES;
+    }();
+    p->bulk_min_bytes = bulk_min;
+  }
   // Work split: one unit per CTA, about two CTAs per SM (two slots stay free:
   // one for the poller CTA of the fused launch).  Units are token groups; with
   // few tokens every group is further split along the hidden dimension so that
@@ -772,7 +846,12 @@ extern "C" int kb_a2a_dispatch(const KbA2aArgs* a, void* stream) {
   A2aParams p;
   rc = fill_params(a, &p, sms);
   if (rc != KB_OK) return rc;
-  const size_t smem = (3 * p.E + 2 * MAX_ENT_PER_CTA) * sizeof(int32_t);
+  const size_t smem = dispatch_smem_bytes(p.E);
+  static bool attr_set = false;
+  if (!attr_set) {
+    KB_CUDA_OK(cudaFuncSetAttribute(a2a_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dispatch_smem_bytes(MAX_EXPERTS)));
+    attr_set = true;
+  }
   a2a_dispatch_kernel<<<p.tok_groups * p.h_splits, A2A_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p);
   KB_CUDA_OK(cudaGetLastError());
   return KB_OK;
@@ -832,9 +911,12 @@ extern "C" int kb_a2a_combine(const KbA2aArgs* a, void* stream) {
 
 template <typename T>
 static int launch_fused(const A2aParams& p, int sms, cudaStream_t st) {
-  const size_t smem_d = (3 * p.E + 2 * MAX_ENT_PER_CTA) * sizeof(int32_t);
-  const size_t smem_e = p.E * sizeof(int32_t);
-  const size_t smem = smem_d > smem_e ? smem_d : smem_e;
+  const size_t smem = dispatch_smem_bytes(p.E);  // the expert and combine phases reuse the front of it
+  static bool attr_set = false;
+  if (!attr_set) {
+    KB_CUDA_OK(cudaFuncSetAttribute(a2a_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dispatch_smem_bytes(MAX_EXPERTS)));
+    attr_set = true;
+  }
   // The occupancy query costs microseconds of host time; its answer depends only
   // on the kernel instance and the shared-memory size.
   static size_t cached_smem = ~size_t(0);
