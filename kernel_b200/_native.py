@@ -85,6 +85,8 @@ class A2aArgs(C.Structure):
         ("wait_limit_ns", C.c_uint64),
         ("num_ctas", C.c_int),
         ("trace", C.c_void_p),
+        ("meta_off", C.c_uint64),
+        ("rank_slots", C.c_void_p),
     ]
 
 
@@ -122,6 +124,7 @@ def _declare(lib: C.CDLL) -> None:
         "kb_gemm_ag_flag_bytes": (u64, [i, i]),
         "kb_gemm_ag_counter_bytes": (u64, [i, i]),
         "kb_a2a_rows_bytes": (u64, [i, i, i, i, i]),
+        "kb_a2a_meta_bytes": (u64, [i, i, i]),
         "kb_a2a_flag_bytes": (u64, []),
         "kb_a2a_sync_bytes": (u64, []),
         "kb_a2a_flag_stride_words": (i, []),

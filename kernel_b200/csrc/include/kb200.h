@@ -155,9 +155,12 @@ typedef struct KbA2aArgs {
   uint64_t wait_limit_ns;
   int num_ctas;
   uint64_t* trace;      // optional device uint64[16]: globaltimer stamps of CTA 0 at the phase boundaries
+  uint64_t meta_off;    // kb_a2a_meta_bytes(): expert lists and weights of the one-launch round trip's unique rows
+  int32_t* rank_slots;  // local scratch [max_tokens * world] of the one-launch round trip
 } KbA2aArgs;
 
 uint64_t kb_a2a_rows_bytes(int world, int max_tokens, int topk, int hidden, int elem_bytes);
+uint64_t kb_a2a_meta_bytes(int world, int max_tokens, int topk);
 uint64_t kb_a2a_flag_bytes(void);
 uint64_t kb_a2a_sync_bytes(void);
 int kb_a2a_flag_stride_words(void);

@@ -39,6 +39,15 @@ constexpr int MAX_ENT_PER_CTA = 2048;
 // destinations with one cp.async.bulk each.
 constexpr int ROWBUF_BYTES = 16384;
 constexpr int BULK_MIN_BYTES = 1024;  // shorter slices go the load / store way
+constexpr int DEDUP_MAX_SLOTS = 4096;  // one-launch round trip: (tokens of a CTA) x world entries of its slot table
+
+// Words of the integer tables at the front of the dynamic shared memory of a
+// kernel that runs a dispatch phase (the row buffers follow them).
+__host__ __device__ inline int table_ints(int experts) {
+  const int a = 3 * experts + 2 * MAX_ENT_PER_CTA;  // per-expert dispatch: tot, pre, off, entry experts, entry slots
+  const int b = 32 + 2 * DEDUP_MAX_SLOTS;           // per-rank dispatch: pre[16], tot[16], slot table, rank masks
+  return a > b ? a : b;
+}
 // Every (phase, source) flag sits on a 128-byte line of its own: a peer's flag
 // store never queues behind polls of another source's flag.
 constexpr int FLAG_STRIDE_WORDS = 32;
@@ -63,6 +72,9 @@ struct A2aParams {
   uint64_t limit_ns;
   uint64_t* trace;
   int bulk_min_bytes;  // row slices at least this long are pushed by the bulk-copy engine; 0x7fffffff: never
+  int tmax;            // max_tokens: capacity, in unique rows, of one source's share of a receive region
+  uint64_t meta_off;   // one-launch round trip: [world][tmax][2k + 2] words, expert lists and weights of the unique rows
+  int32_t* rank_slots; // one-launch round trip: local [T][world], slot of (token, rank) or -1
 };
 
 // Phase stamps (nanoseconds of the global timer) written by thread 0 of CTA 0.
@@ -199,7 +211,7 @@ __device__ __forceinline__ void expert_offsets(const int32_t* tot, int32_t* off,
 
 __device__ __forceinline__ void dispatch_body(const A2aParams& p, int32_t* sh, int nworkers) {
   // behind the tables: two row buffers (128-byte aligned) and their two mbarriers
-  uint8_t* rowbuf = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sh + 3 * p.E + 2 * MAX_ENT_PER_CTA) + 127) & ~uintptr_t(127));
+  uint8_t* rowbuf = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sh + table_ints(p.E)) + 127) & ~uintptr_t(127));
   uint64_t* rowbar = reinterpret_cast<uint64_t*>(rowbuf + 2 * ROWBUF_BYTES);
   if (threadIdx.x == 0) {
     kb::mbar_init(&rowbar[0], 1);
@@ -664,11 +676,14 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_combine_kernel(const A2aParam
   combine_body<T, false>(p, sh, sh + MAX_ENT_PER_CTA);
 }
 
+#include "a2a_dedup.cuh"
+
 // All three phases in one cooperative launch (every CTA is resident, so CTAs may
 // wait for one another).  The last CTA of the grid is the poller: it moves no
 // rows, it is the only reader of the flag lines the peers write and republishes
 // them locally.  The other CTAs are the data CTAs; their phases are separated
 // only by the arrival words, this rank's own flags doubling as grid barrier.
+// The phases are the per-rank ones of a2a_dedup.cuh: one row per (token, rank).
 template <typename T>
 __global__ void __launch_bounds__(A2A_THREADS) a2a_fused_kernel(const A2aParams p) {
   extern __shared__ int32_t sh[];
@@ -677,11 +692,11 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_fused_kernel(const A2aParams 
     poller_body(p);
     return;
   }
-  dispatch_body(p, sh, nworkers);
+  dispatch_dedup_body(p, sh, nworkers);
   __syncthreads();
-  expert_body<T, true>(p, sh, nworkers);  // uses the first E words only: the entry tables behind them stay intact
+  expert_dedup_body<T>(p, nworkers);  // leaves the dynamic shared memory alone: the slot table stays intact
   __syncthreads();
-  combine_body<T, true>(p, sh + 3 * p.E, sh + 3 * p.E + MAX_ENT_PER_CTA);
+  combine_dedup_body<T>(p, sh + 32);
 }
 
 // --------------------------------------------------------------- small utils ----
@@ -725,7 +740,7 @@ __global__ void post_ready_kernel(const A2aParams p) {
 // Dynamic shared memory of a kernel that runs the dispatch phase: the five tables,
 // alignment slack, two row buffers, two mbarriers.
 size_t dispatch_smem_bytes(int experts) {
-  return (3 * static_cast<size_t>(experts) + 2 * MAX_ENT_PER_CTA) * sizeof(int32_t) + 128 + 2 * ROWBUF_BYTES + 16;
+  return static_cast<size_t>(table_ints(experts)) * sizeof(int32_t) + 128 + 2 * ROWBUF_BYTES + 16;
 }
 
 int fill_params(const KbA2aArgs* a, A2aParams* p, int sms) {
@@ -787,6 +802,9 @@ int fill_params(const KbA2aArgs* a, A2aParams* p, int sms) {
   p->status = a->status;
   p->limit_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
   p->trace = a->trace;
+  p->tmax = a->max_tokens;
+  p->meta_off = a->meta_off;
+  p->rank_slots = a->rank_slots;
   {
     static const int bulk_min = [] {
       const char* v = getenv("KB200_A2A_BULK");  // 0: ordinary loads and stores only
@@ -833,6 +851,11 @@ int device_sms(int* sms) {
 extern "C" uint64_t kb_a2a_flag_bytes(void) { return 2ull * KB_MAX_WORLD * FLAG_STRIDE_WORDS * 4; }
 extern "C" uint64_t kb_a2a_sync_bytes(void) { return 512; }
 extern "C" int kb_a2a_flag_stride_words(void) { return FLAG_STRIDE_WORDS; }
+
+extern "C" uint64_t kb_a2a_meta_bytes(int world, int max_tokens, int topk) {
+  const uint64_t b = (uint64_t)world * max_tokens * (2 * topk + 2) * 4;
+  return (b + 255) / 256 * 256;
+}
 
 extern "C" uint64_t kb_a2a_rows_bytes(int world, int max_tokens, int topk, int hidden, int elem_bytes) {
   const uint64_t b = (uint64_t)world * max_tokens * topk * hidden * elem_bytes;
@@ -911,7 +934,18 @@ extern "C" int kb_a2a_combine(const KbA2aArgs* a, void* stream) {
 
 template <typename T>
 static int launch_fused(const A2aParams& p, int sms, cudaStream_t st) {
-  const size_t smem = dispatch_smem_bytes(p.E);  // the expert and combine phases reuse the front of it
+  if (p.meta_off == 0 || p.rank_slots == nullptr) {
+    kb::set_error("a2a fused: the workspace has no per-rank metadata region (meta_off, rank_slots)");
+    return KB_ERR_UNSUPPORTED;
+  }
+  {
+    const int tok_per = ((p.T > 0 ? p.T : 1) + p.tok_groups - 1) / p.tok_groups;
+    if (tok_per * p.world > DEDUP_MAX_SLOTS) {
+      kb::set_error("a2a fused: %d tokens per CTA x %d ranks exceed the slot table", tok_per, p.world);
+      return KB_ERR_UNSUPPORTED;
+    }
+  }
+  const size_t smem = dispatch_smem_bytes(p.E);  // the combine phase reuses the slot table at the front of it
   static bool attr_set = false;
   if (!attr_set) {
     KB_CUDA_OK(cudaFuncSetAttribute(a2a_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dispatch_smem_bytes(MAX_EXPERTS)));

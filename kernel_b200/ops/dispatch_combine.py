@@ -72,7 +72,8 @@ class MoEAllToAll:
             rows = int(lib.kb_a2a_rows_bytes(self.world, max_num_tokens, experts_per_token, hidden_dim, eb))
             counts = (self.world * self.El * 4 + 255) // 256 * 256
             flag_bytes, sync_bytes = int(lib.kb_a2a_flag_bytes()), int(lib.kb_a2a_sync_bytes())
-            need = 2 * rows + counts + flag_bytes + sync_bytes + 4096
+            meta_bytes = int(lib.kb_a2a_meta_bytes(self.world, max_num_tokens, experts_per_token))
+            need = 2 * rows + counts + flag_bytes + sync_bytes + meta_bytes + 4096
             # no multicast mapping here: these kernels use peer loads and stores only
             self.heap = heap or (SymmHeap(need, group=group, device=device, nvls=False) if self.native
                                  else SymmHeap(need, group=group, backend="host", timeout_s=_WAIT_LIMIT_NS / 1e9 + 5))
@@ -81,7 +82,9 @@ class MoEAllToAll:
             self.count_off = self.heap.alloc(counts)
             self.flag_off = self.heap.alloc(flag_bytes)
             self.sync_off = self.heap.alloc(sync_bytes)
+            self.meta_off = self.heap.alloc(meta_bytes)  # expert lists and weights of the one-launch round trip's rows
             self._flag_stride = int(lib.kb_a2a_flag_stride_words())
+            self.rank_slots = torch.empty(max_num_tokens * self.world, dtype=torch.int32, device=self.heap.device)
             self.slots = torch.empty(self.cap, dtype=torch.int32, device=self.heap.device)
             self.status = self.heap.status
             self._eb = eb
@@ -111,6 +114,8 @@ class MoEAllToAll:
         a.status = self.status.data_ptr()
         a.wait_limit_ns = _WAIT_LIMIT_NS
         a.trace = self._trace.data_ptr() if self._trace is not None else None
+        a.meta_off = self.meta_off
+        a.rank_slots = self.rank_slots.data_ptr()
         return a
 
     # -------------------------------------------------------------- tracing ----

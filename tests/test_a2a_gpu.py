@@ -113,10 +113,13 @@ def test_argument_validation():
         ctx.dispatch_scale_combine(x5, idx5, w5)
 
 
-def test_sentinel_and_guard_rows_after_dispatch():
+def test_sentinel_and_guard_rows_after_dispatch(monkeypatch):
     """Poisoned workspace: every row the counts declare valid was written, nothing
-    else was touched (the role a memory checker would play)."""
+    else was touched (the role a memory checker would play).  Runs the three-launch
+    path, whose receive layout (rows grouped by expert) the check understands."""
     from kernel_b200.ops.dispatch_combine import MoEAllToAll
+
+    monkeypatch.setenv("KB200_A2A_FUSED", "0")
 
     E, k, H, T = 32, 4, 1024, 50
     dev = torch.device("cuda")
