@@ -26,7 +26,9 @@ def test_a2a_roofline_and_single_rank():
     r = rf.a2a_roofline_us(256, 8, 7168, 2, 8)
     assert math.isclose(r["link_bytes"], 2 * 25.69e6, rel_tol=1e-3)
     assert math.isclose(r["roofline_us"], 57.1, rel_tol=2e-3)
-    assert rf.a2a_roofline_us(256, 8, 7168, 2, 1)["roofline_us"] == 0.0  # nothing crosses a link on one rank
+    one = rf.a2a_roofline_us(256, 8, 7168, 2, 1)
+    assert one["link_us"] == 0.0  # nothing crosses a link on one rank: the six passes over the rows bound the op
+    assert math.isclose(one["memory_bytes"], (2 * 256 + 4 * 2048) * 7168 * 2) and one["roofline_us"] == one["memory_us"] > 0
 
 
 def test_small_gemm_is_link_bound():

@@ -37,9 +37,12 @@ def test_gemm_kernel_uses_tcgen05_and_tma():
 
 def test_every_wait_is_bounded():
     text = (CSRC / "common" / "ptx.cuh").read_text()
-    # the only spin loops live in the two bounded helpers
-    assert text.count("while (") + text.count("for (;;)") == 2
-    assert "limit_ns" in text
+    # the only spin loops live in the three bounded helpers (mbarrier, mbarrier with
+    # cluster-scope acquire, flag), each of which takes a time limit
+    assert text.count("while (") + text.count("for (;;)") == 3
+    for helper in ("mbar_wait_bounded(", "mbar_wait_bounded_cluster(", "wait_flag_ge("):
+        head = text[text.index("bool " + helper):]
+        assert "limit_ns" in head[:head.index(")")]
 
 
 @pytest.mark.skipif(shutil.which("nvcc") is None and not Path("/usr/local/cuda/bin/nvcc").exists(), reason="no nvcc")
