@@ -79,7 +79,9 @@ struct A2aParams {
 
 // Phase stamps (nanoseconds of the global timer) written by thread 0 of CTA 0.
 // Words 10 and 11 hold the time that CTA spent inside the arrival waits of the
-// expert pass and of the combine.
+// expert pass and of the combine; words 12 to 15 are written by the CTA that
+// finishes a phase last: when it arrived and when it had stored the flags, for
+// the dispatch and for the expert phase.
 enum Stamp { ST_ENTRY = 0, ST_SLOTS = 1, ST_PUSHED = 2, ST_DISPATCH_FLAG = 3, ST_EXPERT_GO = 4, ST_EXPERT_ROWS = 5,
              ST_EXPERT_FLAG = 6, ST_COMBINE_GO = 7, ST_DONE = 8, ST_WAITED_EXPERT = 10, ST_WAITED_COMBINE = 11 };
 __device__ __forceinline__ void stamp(const A2aParams& p, int which) {
@@ -118,6 +120,7 @@ __device__ __forceinline__ void finish_phase(const A2aParams& p, uint32_t* count
     fence_for(p);
     const uint32_t old = atomicAdd(counter, 1u);
     if (old == total - 1u) {
+      if (p.trace != nullptr) p.trace[12 + 2 * which] = kb::globaltimer_ns();  // the last CTA of the phase has arrived
       *counter = 0u;  // ready for the next launch
       fence_for(p);
       for (int dst = 0; dst < p.world; ++dst) {
@@ -125,6 +128,7 @@ __device__ __forceinline__ void finish_phase(const A2aParams& p, uint32_t* count
         if (p.world == 1) kb::st_release_gpu_u32(f, p.epoch);
         else kb::st_relaxed_sys_u32(f, p.epoch);
       }
+      if (p.trace != nullptr) p.trace[13 + 2 * which] = kb::globaltimer_ns();  // its flags are on their way
     }
   }
   __syncthreads();

@@ -138,6 +138,9 @@ class MoEAllToAll:
         out = {name: (t[i + 1] - t[i]) / 1e3 for i, name in enumerate(self.TRACE_PHASES)}
         out["waited_in_expert_pass"] = t[10] / 1e3
         out["waited_for_combine"] = t[11] / 1e3
+        # the CTA that finishes a phase last: when it arrived and when its flags were out, after the kernel's entry
+        for name, i in (("dispatch_last_cta", 12), ("dispatch_flags_out", 13), ("expert_last_cta", 14), ("expert_flags_out", 15)):
+            out[name] = (t[i] - t[0]) / 1e3
         out["total"] = (t[8] - t[0]) / 1e3
         return out
 
