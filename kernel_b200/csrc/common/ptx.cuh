@@ -50,14 +50,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread may stay suspended for up to
+// `hint_ns` before the instruction returns false; the phase's completion wakes it.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Waits until the barrier's phase with the given parity has completed, or until
 // `limit_ns` has elapsed.  Returns false on expiry (caller must unwind).
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
+// `hint_ns` > 0: a role that can afford it (an epilogue warp waiting for a whole
+// tile, a producer waiting for a stage) lets the hardware suspend it between polls
+// instead of issuing a poll every few cycles; the issue slots and the energy of a
+// persistent kernel's idle roles are not free under a power cap.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint64_t limit_ns, uint32_t hint_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3ffu) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
+  while (!(hint_ns ? mbar_try_wait_hint(bar, parity, hint_ns) : mbar_try_wait(bar, parity))) {
+    if ((++spins & (hint_ns ? 0xfu : 0x3ffu)) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
   }
   return true;
 }

@@ -444,7 +444,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           if (mb < 256) ready_mask[mb >> 6] |= 1ull << (mb & 63);
         }
         for (int kb_i = 0; kb_i < p.KB; ++kb_i) {
-          if (!kb::mbar_wait_bounded(&sm.empty[s], ph ^ 1u, p.limit_ns)) {
+          if (!kb::mbar_wait_bounded(&sm.empty[s], ph ^ 1u, p.limit_ns, 400)) {
             kb::report_status(p.status, KB_DEV_TIMEOUT_MBAR, SITE_PROD_EMPTY, (uint32_t)pos, p.epoch);
             *sm.abort = 1;
             ok = false;
@@ -580,7 +580,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t aph = (it >> 1) & 1u;
       // After a failed wait the loop keeps its shape (the named barriers below
       // must be reached by all four warps) but stops waiting.
-      if (*sm.abort == 0 && !kb::mbar_wait_bounded(&sm.tfull[acc], aph, p.limit_ns)) {
+      if (*sm.abort == 0 && !kb::mbar_wait_bounded(&sm.tfull[acc], aph, p.limit_ns, 2000)) {
         kb::report_status(p.status, KB_DEV_TIMEOUT_MBAR, SITE_EPI_TFULL, (uint32_t)pos, p.epoch);
         *sm.abort = 1;
       }
