@@ -87,6 +87,8 @@ class A2aArgs(C.Structure):
         ("trace", C.c_void_p),
         ("meta_off", C.c_uint64),
         ("rank_slots", C.c_void_p),
+        ("ll_off", C.c_uint64),
+        ("ll_max_tokens", C.c_int),
     ]
 
 
@@ -125,6 +127,8 @@ def _declare(lib: C.CDLL) -> None:
         "kb_gemm_ag_counter_bytes": (u64, [i, i]),
         "kb_a2a_rows_bytes": (u64, [i, i, i, i, i]),
         "kb_a2a_meta_bytes": (u64, [i, i, i]),
+        "kb_a2a_ll_max_tokens": (i, []),
+        "kb_a2a_ll_bytes": (u64, [i, i, i, i, i]),
         "kb_a2a_flag_bytes": (u64, []),
         "kb_a2a_sync_bytes": (u64, []),
         "kb_a2a_flag_stride_words": (i, []),

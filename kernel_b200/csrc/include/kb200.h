@@ -157,10 +157,16 @@ typedef struct KbA2aArgs {
   uint64_t* trace;      // optional device uint64[16]: globaltimer stamps of CTA 0 at the phase boundaries
   uint64_t meta_off;    // kb_a2a_meta_bytes(): expert lists and weights of the one-launch round trip's unique rows
   int32_t* rank_slots;  // local scratch [max_tokens * world] of the one-launch round trip
+  uint64_t ll_off;      // kb_a2a_ll_bytes(): landing areas of the low-latency round trip; 0 = not allocated
+  int ll_max_tokens;    // rows per source those areas were sized for (the context's max_tokens)
 } KbA2aArgs;
 
 uint64_t kb_a2a_rows_bytes(int world, int max_tokens, int topk, int hidden, int elem_bytes);
 uint64_t kb_a2a_meta_bytes(int world, int max_tokens, int topk);
+// Low-latency round trip (contexts of at most kb_a2a_ll_max_tokens() tokens per rank): bytes of its landing
+// areas, 0 when max_tokens is too large for it.
+int kb_a2a_ll_max_tokens(void);
+uint64_t kb_a2a_ll_bytes(int world, int max_tokens, int topk, int hidden, int elem_bytes);
 uint64_t kb_a2a_flag_bytes(void);
 uint64_t kb_a2a_sync_bytes(void);
 int kb_a2a_flag_stride_words(void);

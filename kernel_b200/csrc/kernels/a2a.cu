@@ -75,6 +75,8 @@ struct A2aParams {
   int tmax;            // max_tokens: capacity, in unique rows, of one source's share of a receive region
   uint64_t meta_off;   // one-launch round trip: [world][tmax][2k + 2] words, expert lists and weights of the unique rows
   int32_t* rank_slots; // one-launch round trip: local [T][world], slot of (token, rank) or -1
+  uint64_t ll_off;     // low-latency round trip: landing areas in the wire format of a2a_ll.cuh; 0: none
+  int ll_tmax;         // rows per source those areas hold
 };
 
 // Phase stamps (nanoseconds of the global timer) written by thread 0 of CTA 0.
@@ -681,6 +683,7 @@ __global__ void __launch_bounds__(A2A_THREADS) a2a_combine_kernel(const A2aParam
 }
 
 #include "a2a_dedup.cuh"
+#include "a2a_ll.cuh"
 
 // All three phases in one cooperative launch (every CTA is resident, so CTAs may
 // wait for one another).  The last CTA of the grid is the poller: it moves no
@@ -809,6 +812,8 @@ int fill_params(const KbA2aArgs* a, A2aParams* p, int sms) {
   p->tmax = a->max_tokens;
   p->meta_off = a->meta_off;
   p->rank_slots = a->rank_slots;
+  p->ll_off = a->ll_off;
+  p->ll_tmax = a->ll_max_tokens;
   {
     static const int bulk_min = [] {
       const char* v = getenv("KB200_A2A_BULK");  // 0: ordinary loads and stores only
@@ -858,6 +863,13 @@ extern "C" int kb_a2a_flag_stride_words(void) { return FLAG_STRIDE_WORDS; }
 
 extern "C" uint64_t kb_a2a_meta_bytes(int world, int max_tokens, int topk) {
   const uint64_t b = (uint64_t)world * max_tokens * (2 * topk + 2) * 4;
+  return (b + 255) / 256 * 256;
+}
+
+extern "C" int kb_a2a_ll_max_tokens(void) { return LL_MAX_TOKENS; }
+extern "C" uint64_t kb_a2a_ll_bytes(int world, int max_tokens, int topk, int hidden, int elem_bytes) {
+  if (max_tokens > LL_MAX_TOKENS) return 0;
+  const uint64_t b = ll_region_bytes(world, max_tokens, topk, hidden * elem_bytes);
   return (b + 255) / 256 * 256;
 }
 
@@ -977,6 +989,23 @@ static int launch_fused(const A2aParams& p, int sms, cudaStream_t st) {
   return KB_OK;
 }
 
+// The low-latency kernel's CTAs poll data that other CTAs of peer ranks produce only after
+// they themselves have been served by this rank: all of them must be resident.
+template <typename T>
+static int launch_ll(const A2aParams& p, int sms, cudaStream_t st) {
+  static int per_sm = 0;
+  if (per_sm == 0) KB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, a2a_ll_kernel<T>, A2A_THREADS, 0));
+  const int units = p.tok_groups * p.h_splits;
+  if (per_sm < 1 || units > per_sm * sms) {
+    kb::set_error("a2a low-latency: %d CTAs cannot be co-resident (%d per SM)", units, per_sm);
+    return KB_ERR_UNSUPPORTED;
+  }
+  A2aParams copy = p;
+  void* args[] = {&copy};
+  KB_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(a2a_ll_kernel<T>), dim3(units), dim3(A2A_THREADS), args, 0, st));
+  return KB_OK;
+}
+
 extern "C" int kb_a2a_round_trip(const KbA2aArgs* a, void* stream) {
   int sms = 0;
   int rc = device_sms(&sms);
@@ -985,6 +1014,14 @@ extern "C" int kb_a2a_round_trip(const KbA2aArgs* a, void* stream) {
   rc = fill_params(a, &p, sms);
   if (rc != KB_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The choice must be the same on every rank, so it depends on the context's capacity, not on this call's tokens.
+  if (p.ll_off != 0 && p.ll_tmax >= p.tmax && p.tmax <= LL_MAX_TOKENS && p.T <= p.ll_tmax) {
+    switch (a->dtype) {
+      case 0: return launch_ll<__nv_bfloat16>(p, sms, st);
+      case 1: return launch_ll<__half>(p, sms, st);
+      case 2: return launch_ll<float>(p, sms, st);
+    }
+  }
   switch (a->dtype) {
     case 0: return launch_fused<__nv_bfloat16>(p, sms, st);
     case 1: return launch_fused<__half>(p, sms, st);

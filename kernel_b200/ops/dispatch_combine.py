@@ -58,6 +58,8 @@ class MoEAllToAll:
         self.cap = max_num_tokens * experts_per_token
         self.native = torch.cuda.is_available() and (device is None or torch.device(device).type == "cuda")
         self.epoch = 0
+        self.low_latency = False
+        self.ll_off = 0
         self.heap = None
         self._trace = None
         # CPU ranks: the same protocol over a memfd-backed symmetric heap (bf16, fp16,
@@ -73,7 +75,11 @@ class MoEAllToAll:
             counts = (self.world * self.El * 4 + 255) // 256 * 256
             flag_bytes, sync_bytes = int(lib.kb_a2a_flag_bytes()), int(lib.kb_a2a_sync_bytes())
             meta_bytes = int(lib.kb_a2a_meta_bytes(self.world, max_num_tokens, experts_per_token))
-            need = 2 * rows + counts + flag_bytes + sync_bytes + meta_bytes + 4096
+            # small contexts get the landing areas of the low-latency round trip (flags inside the data)
+            ll_bytes = 0
+            if self.native and os.environ.get("KB200_A2A_LL", "1") == "1":
+                ll_bytes = int(lib.kb_a2a_ll_bytes(self.world, max_num_tokens, experts_per_token, hidden_dim, eb))
+            need = 2 * rows + counts + flag_bytes + sync_bytes + meta_bytes + ll_bytes + 8192
             # no multicast mapping here: these kernels use peer loads and stores only
             self.heap = heap or (SymmHeap(need, group=group, device=device, nvls=False) if self.native
                                  else SymmHeap(need, group=group, backend="host", timeout_s=_WAIT_LIMIT_NS / 1e9 + 5))
@@ -83,6 +89,8 @@ class MoEAllToAll:
             self.flag_off = self.heap.alloc(flag_bytes)
             self.sync_off = self.heap.alloc(sync_bytes)
             self.meta_off = self.heap.alloc(meta_bytes)  # expert lists and weights of the one-launch round trip's rows
+            self.ll_off = self.heap.alloc(ll_bytes) if ll_bytes else 0
+            self.low_latency = bool(self.ll_off)  # round trips of this context poll the data, not flags
             self._flag_stride = int(lib.kb_a2a_flag_stride_words())
             self.rank_slots = torch.empty(max_num_tokens * self.world, dtype=torch.int32, device=self.heap.device)
             self.slots = torch.empty(self.cap, dtype=torch.int32, device=self.heap.device)
@@ -116,6 +124,7 @@ class MoEAllToAll:
         a.trace = self._trace.data_ptr() if self._trace is not None else None
         a.meta_off = self.meta_off
         a.rank_slots = self.rank_slots.data_ptr()
+        a.ll_off, a.ll_max_tokens = self.ll_off, (self.max_tokens if self.ll_off else 0)
         return a
 
     # -------------------------------------------------------------- tracing ----

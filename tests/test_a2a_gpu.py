@@ -83,6 +83,33 @@ def test_split_dispatch_expert_combine_api():
     assert torch.allclose(out.float(), ref, rtol=1e-2, atol=5e-3)
 
 
+@pytest.mark.parametrize("T", [0, 1, 16, 32])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_low_latency_path_equals_regular_path(T, dtype, monkeypatch):
+    """Contexts of at most 32 tokens per rank take the flag-in-data kernel; its
+    rounding points are those of the regular one-launch kernel, so the outputs are
+    equal bit for bit, call after call (the count lines alternate with the epoch)."""
+    from kernel_b200.ops.dispatch_combine import MoEAllToAll
+
+    dev = torch.device("cuda")
+    E, k, H = 64, 8, 7168
+    x, idx, w = _inputs(E, k, H, T, dtype, dev, seed=T)
+    ll = MoEAllToAll(E, k, H, 32, dtype=dtype, device=dev)
+    assert ll.low_latency
+    monkeypatch.setenv("KB200_A2A_LL", "0")
+    regular = MoEAllToAll(E, k, H, 32, dtype=dtype, device=dev)
+    assert not regular.low_latency
+    want = regular.dispatch_scale_combine(x, idx, w, 2)
+    for _ in range(3):
+        got = ll.dispatch_scale_combine(x, idx, w, 2)
+        assert torch.equal(got, want)
+    torch.cuda.synchronize()
+    ll.heap.check_status()
+    ref = _expected(x, idx, w, E, 2)
+    tol = dict(rtol=1e-2, atol=5e-3) if dtype != torch.float32 else dict(rtol=1e-5, atol=1e-6)
+    assert torch.allclose(got.float(), ref, **tol)
+
+
 def test_out_of_range_expert_is_reported_not_written():
     from kernel_b200 import _native as N
     from kernel_b200.ops.dispatch_combine import MoEAllToAll
