@@ -26,6 +26,13 @@ class NativeError(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__(f"libkb200 status {code}: {message}")
         self.code = code
+        self.message = message
+
+    def __reduce__(self):
+        # Exceptions cross process boundaries (a pool worker's error travels to the
+        # evaluator pickled); the default reduction would call __init__ with the one
+        # formatted string and fail on the receiving side.
+        return (type(self), (self.code, self.message))
 
 
 class SymmTimeoutError(NativeError):

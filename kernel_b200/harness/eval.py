@@ -37,7 +37,9 @@ import importlib.util
 import json
 import math
 import multiprocessing
+import functools
 import os
+import signal
 import socket
 import sys
 import time
@@ -185,6 +187,42 @@ def _sync(device: torch.device) -> None:
         torch.cuda.synchronize(device)
 
 
+FAIL_GRACE_S = float(os.environ.get("KB200_EVAL_FAIL_GRACE_S", "10"))
+
+
+class WorkerFailure(str):
+    """What a worker returns instead of raising: the error as text.  An exception
+    object may not survive the trip back to the evaluator (one whose constructor
+    takes other arguments than ``args`` breaks the pool's result thread, and the
+    evaluator then waits for a result that never comes)."""
+
+
+def _reports_errors(fn):
+    @functools.wraps(fn)
+    def guarded(*args, **kwargs):
+        try:
+            return fn(*args, **kwargs)
+        except BaseException as e:  # noqa: BLE001 - the text goes back to the evaluator
+            return WorkerFailure(f"{type(e).__name__}: {e}")
+
+    return guarded
+
+
+def _raise_fd_limit() -> None:
+    """A pool worker lives through one process group per case, and a communicator
+    over eight GPUs holds descriptors per peer; the soft limit of 1024 that
+    containers start with is lifted to the hard limit once per worker."""
+    try:
+        import resource
+
+        soft, hard = resource.getrlimit(resource.RLIMIT_NOFILE)
+        want = hard if hard != resource.RLIM_INFINITY else 1 << 20
+        if soft != resource.RLIM_INFINITY and soft < want:
+            resource.setrlimit(resource.RLIMIT_NOFILE, (want, hard))
+    except (ImportError, ValueError, OSError):
+        pass
+
+
 class _Group:
     """Process-group lifetime of one test, as in ``eval.py:167-184`` of the reference."""
 
@@ -196,6 +234,7 @@ class _Group:
     def __enter__(self):
         import torch.distributed as dist
 
+        _raise_fd_limit()
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(self.cfg.port)
         kwargs = {}
@@ -231,6 +270,7 @@ def _any_failed(failed: bool, device: torch.device) -> bool:
 
 
 # --------------------------------------------------------------------- test ----
+@_reports_errors
 def run_distributed_test(cfg: RunConfig, test: TestCase, rank: int) -> Tuple[bool, str]:
     world = test.args["world_size"]
     with _Group(cfg, rank, world) as g:
@@ -243,6 +283,7 @@ def run_distributed_test(cfg: RunConfig, test: TestCase, rank: int) -> Tuple[boo
         return wrap_check(ref, data, out)
 
 
+@_reports_errors
 def run_local_test(cfg: RunConfig, test: TestCase) -> Tuple[bool, str]:
     device = torch.device("cuda", 0) if cfg.backend == "nccl" else torch.device("cpu")
     ref, sub = cfg.modules()
@@ -272,6 +313,7 @@ def _timed_call(fn, device: torch.device) -> Tuple[Any, float]:
     return out, float(time.perf_counter_ns() - t0)
 
 
+@_reports_errors
 def run_distributed_benchmark(cfg: RunConfig, test: TestCase, rank: int, recheck: bool, max_repeats: int,
                               max_time_ns: float):
     import torch.distributed as dist
@@ -319,6 +361,7 @@ def run_distributed_benchmark(cfg: RunConfig, test: TestCase, rank: int, recheck
         return calculate_stats(durations)
 
 
+@_reports_errors
 def run_local_benchmark(cfg: RunConfig, test: TestCase, recheck: bool, max_repeats: int, max_time_ns: float):
     dev = torch.device("cuda", 0) if cfg.backend == "nccl" else torch.device("cpu")
     ref, sub = cfg.modules()
@@ -353,6 +396,7 @@ def run_local_benchmark(cfg: RunConfig, test: TestCase, recheck: bool, max_repea
 
 
 # ------------------------------------------------------------------ profile ----
+@_reports_errors
 def run_profile(cfg: RunConfig, test: TestCase, rank: int) -> str:
     from torch.profiler import ProfilerActivity, profile
 
@@ -438,6 +482,38 @@ class Runner:
             raise SpecError(f"world_size {world} exceeds the {self.n_gpus} worker processes (POPCORN_GPUS)")
         return world
 
+    def _collect(self, pending, limit_s: float):
+        """Results of the per-rank workers in rank order.  Waits ``limit_s`` for all
+        of them, but once one rank has failed only ``FAIL_GRACE_S`` longer: its peers
+        sit in a collective or a device-side wait that nobody will complete.  A rank
+        without a result gets a ``WorkerFailure`` and the pool is rebuilt."""
+        t_end = time.monotonic() + limit_s
+        results: List[Any] = [None] * len(pending)
+        have = [False] * len(pending)
+        failed_at = None
+        while not all(have):
+            for i, p in enumerate(pending):
+                if have[i] or not p.ready():
+                    continue
+                try:
+                    results[i] = p.get(0)
+                except Exception as e:  # the result could not be delivered as sent
+                    results[i] = WorkerFailure(f"{type(e).__name__}: {e}")
+                have[i] = True
+                if isinstance(results[i], WorkerFailure) and failed_at is None:
+                    failed_at = time.monotonic()
+            now = time.monotonic()
+            if all(have) or now > t_end or (failed_at is not None and now > failed_at + FAIL_GRACE_S):
+                break
+            time.sleep(0.02)
+        if not all(have):
+            why = f"timed out after {limit_s:g} s" if failed_at is None else "no result: a peer rank failed"
+            for i in range(len(pending)):
+                if not have[i]:
+                    results[i] = WorkerFailure(why)
+            self._timed_out()
+        return results
+
     def test(self, test: TestCase) -> Tuple[bool, str]:
         try:
             world = self._world(test)
@@ -445,20 +521,10 @@ class Runner:
             return False, str(e)
         cfg = self._cfg(test)
         if world is None:
-            return self.pool.apply(run_local_test, (cfg, test))
+            res = self.pool.apply(run_local_test, (cfg, test))
+            return (False, str(res)) if isinstance(res, WorkerFailure) else res
         pending = [self.pool.apply_async(run_distributed_test, (cfg, test, r)) for r in range(world)]
-        results = []
-        timed_out = False
-        for r, p in enumerate(pending):
-            try:
-                results.append(p.get(1 if timed_out else TEST_TIMEOUT_S))
-            except multiprocessing.TimeoutError:
-                timed_out = True
-                results.append((False, f"timed out after {TEST_TIMEOUT_S} s"))
-            except Exception as e:  # worker raised
-                results.append((False, f"{type(e).__name__}: {e}"))
-        if timed_out:
-            self._timed_out()
+        results = [(False, str(r)) if isinstance(r, WorkerFailure) else r for r in self._collect(pending, TEST_TIMEOUT_S)]
         ok = all(r[0] for r in results)
         errors = "\n".join(f"rank {i} - {r[1]}" for i, r in enumerate(results) if not r[0])
         return ok, errors
@@ -470,21 +536,11 @@ class Runner:
             return str(e)
         cfg = self._cfg(test)
         if world is None:
-            return self.pool.apply(run_local_benchmark, (cfg, test, recheck, max_repeats, max_time_ns))
+            res = self.pool.apply(run_local_benchmark, (cfg, test, recheck, max_repeats, max_time_ns))
+            return str(res) if isinstance(res, WorkerFailure) else res
         pending = [self.pool.apply_async(run_distributed_benchmark, (cfg, test, r, recheck, max_repeats, max_time_ns))
                    for r in range(world)]
-        results = []
-        timed_out = False
-        for p in pending:
-            try:
-                results.append(p.get(1 if timed_out else BENCH_TIMEOUT_S))
-            except multiprocessing.TimeoutError:
-                timed_out = True
-                results.append(f"timed out after {BENCH_TIMEOUT_S} s")
-            except Exception as e:
-                results.append(f"{type(e).__name__}: {e}")
-        if timed_out:
-            self._timed_out()
+        results = self._collect(pending, BENCH_TIMEOUT_S)
         failed = [(i, r) for i, r in enumerate(results) if not isinstance(r, Stats)]
         if failed:
             return "\n".join(f"rank {i} - {msg}" for i, msg in failed)
@@ -494,9 +550,9 @@ class Runner:
         world = self._world(test)
         cfg = self._cfg(test)
         if world is None:
-            return self.pool.apply(run_profile, (cfg, test, 0))
+            return str(self.pool.apply(run_profile, (cfg, test, 0)))
         pending = [self.pool.apply_async(run_profile, (cfg, test, r)) for r in range(world)]
-        return [p.get(BENCH_TIMEOUT_S) for p in pending][0]
+        return str(self._collect(pending, BENCH_TIMEOUT_S)[0])
 
 
 def case_roofline_us(task: str, args: dict) -> Optional[float]:
@@ -657,6 +713,15 @@ def main(argv: Optional[List[str]] = None) -> int:
             if "world_size" in t.args:
                 t.args["world_size"] = ns.world
 
+    def _terminated(signum, frame):
+        # leave through the context managers below: the pool's workers (and what they
+        # hold on the GPUs) must not outlive an evaluator that was told to stop
+        raise SystemExit(128 + signum)
+
+    try:
+        signal.signal(signal.SIGTERM, _terminated)
+    except ValueError:  # not the main thread
+        pass
     with PopcornOutput(int(fd)) as logger:
         with WorkerPool(n_gpus) as pool:
             runner = Runner(pool, n_gpus, ns.task, ns.submission or ns.impl, ns.backend)

@@ -159,3 +159,82 @@ def test_a_case_that_runs_out_of_time_does_not_block_the_next_one(tmp_path):
     assert rc == 112 and log["check"] == "fail"
     assert log["test.0.status"] == "fail" and "timed out" in log["test.0.error"]
     assert log["test.1.status"] == "pass"
+
+
+def test_a_rank_that_raises_a_native_error_is_reported_and_the_next_case_runs(tmp_path):
+    """Rank 1 raises the native library's error type inside the first case.  The
+    error comes back as text (its object would not survive unpickling by default
+    and would stop the pool's result thread), rank 0, left alone in a collective,
+    is given a short grace period and replaced, and the second case passes."""
+    import time
+
+    (tmp_path / "raising_sub.py").write_text(
+        "import torch.distributed as dist\n"
+        "from kernel_b200 import _native as N\n"
+        "from kernel_b200.tasks.gemm_rs.submission import custom_kernel as good\n"
+        "def custom_kernel(data):\n"
+        "    if data[0].shape[0] == 128 and dist.get_rank() == 1:\n"
+        "        raise N.NativeError(N.KB_ERR_ARG, 'made up for the test')\n"
+        "    return good(data)\n")
+    bad = "world_size: 2; m: 128; n: 128; k: 256; has_bias: False; seed: 3"
+    t0 = time.monotonic()
+    rc, log, err = _run(["test", "@tests", "--backend", "gloo", "--submission", "raising_sub"], bad + "\n" + RS + "\n", tmp_path,
+                        env_extra={"PYTHONPATH": f"{ROOT}:{tmp_path}", "KB200_EVAL_TEST_TIMEOUT_S": "300",
+                                   "KB200_EVAL_FAIL_GRACE_S": "5", "KB200_WAIT_LIMIT_MS": "3000"})
+    assert time.monotonic() - t0 < 200          # not the 300 s limit of a silent rank
+    assert rc == 112 and log["check"] == "fail"
+    report = "\n".join(f"{k}: {v}" for k, v in log.items())  # the error has one line per rank
+    assert "rank 1 - NativeError" in report and "made up for the test" in report
+    assert log["test.1.status"] == "pass"
+
+
+def test_native_errors_survive_pickling():
+    import pickle
+
+    from kernel_b200 import _native as N
+
+    for exc in (N.NativeError(N.KB_ERR_ARG, "bad argument"), N.SymmTimeoutError(N.KB_ERR_TIMEOUT, "late peer")):
+        twin = pickle.loads(pickle.dumps(exc))
+        assert type(twin) is type(exc) and twin.code == exc.code and str(twin) == str(exc)
+
+
+def test_sigterm_takes_the_workers_along(tmp_path):
+    """An evaluator that is told to stop (a caller's time limit sends SIGTERM)
+    terminates its pool: no worker is left holding a rendezvous or a device."""
+    import signal
+    import time
+
+    import psutil
+
+    (tmp_path / "sleepy_sub.py").write_text(
+        "import time\n"
+        "def custom_kernel(data):\n"
+        "    time.sleep(600)\n")
+    tests = tmp_path / "tests.txt"
+    tests.write_text(RS + "\n")
+    r, w = os.pipe()
+    env = dict(os.environ, POPCORN_GPUS="2", PYTHONPATH=f"{ROOT}:{tmp_path}", OMP_NUM_THREADS="1", POPCORN_FD=str(w))
+    env.pop("MASTER_PORT", None)
+    proc = subprocess.Popen([sys.executable, "-m", "kernel_b200.harness.eval", "test", str(tests), "--backend", "gloo",
+                             "--submission", "sleepy_sub"], env=env, pass_fds=(w,), cwd=ROOT,
+                            stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    os.close(w)
+    try:
+        parent = psutil.Process(proc.pid)
+        deadline = time.monotonic() + 120
+        workers = []
+        while time.monotonic() < deadline:  # wait until the ranks are inside the submission
+            workers = [c for c in parent.children(recursive=True) if "resource_tracker" not in " ".join(c.cmdline())]
+            if len(workers) >= 2 and all(c.cpu_times().user > 0.5 for c in workers):
+                break
+            time.sleep(0.5)
+        assert len(workers) >= 2
+        time.sleep(3)
+        proc.send_signal(signal.SIGTERM)
+        proc.wait(timeout=60)
+        gone, alive = psutil.wait_procs(workers, timeout=30)
+        assert not alive
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+        os.close(r)
