@@ -145,6 +145,10 @@ def check_implementation(data: input_t, output: output_t):
     guards the typical error: a wrong partial, a dropped tile or a bias applied
     with the wrong factor moves the mean error far beyond the library path's."""
     expected, magnitude = ref_kernel_fp32(data, with_magnitude=True)
+    # The library path is a collective too: it runs before any rank can leave with a
+    # verdict of its own, or the ranks whose shards pass would wait in it for a rank
+    # that has already returned.
+    library = (ref_kernel(data).float() - expected).abs().mean().item()
     if output.device != expected.device:
         return False, f"Output device mismatch: {output.device} != {expected.device}"
     if output.shape != expected.shape:
@@ -155,7 +159,6 @@ def check_implementation(data: input_t, output: output_t):
         i = int(diff.argmax())
         return False, (f"Output values mismatch: {int(bad.sum())} of {bad.numel()} elements, max abs diff "
                        f"{diff.max().item():.5g} at flat index {i} (expected {expected.flatten()[i].item():.5g})")
-    library = (ref_kernel(data).float() - expected).abs().mean().item()
     mine = diff.mean().item()
     floor = 1e-3 * expected.abs().mean().item()
     if not mine <= MEAN_ERROR_FACTOR * library + floor:
