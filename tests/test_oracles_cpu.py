@@ -162,3 +162,24 @@ def test_two_step_dispatch_buffers_gloo_world2():
     res = run_ranks(_two_step_buffers, 2)
     assert all(ok for ok, _ in res)
     assert res[0][1] == 2 * 6 * 2  # every (token, k) copy landed exactly once
+
+
+def _gemm_rs_one_rank_wrong(rank, world):
+    """Rank 0 hands the checker a wrong shard, rank 1 a right one: both get their
+    own verdict and both leave the checker (its collectives do not depend on the
+    verdict), so the barrier behind it is reached."""
+    import torch.distributed as dist
+
+    from kernel_b200.tasks.gemm_rs import reference as R
+
+    data = R.generate_input(rank, world, 64, 128, 256, True, seed=5)
+    out = R.ref_kernel(data)
+    if rank == 0:
+        out = out + 1.0
+    verdict = R.check_implementation(data, out)
+    dist.barrier()
+    return verdict[0]
+
+
+def test_gemm_rs_checker_verdicts_may_differ_between_ranks():
+    assert run_ranks(_gemm_rs_one_rank_wrong, 2, timeout=120) == [False, True]
