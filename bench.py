@@ -80,7 +80,7 @@ class ClockSampler(threading.Thread):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
         self.samples, self.power, self.stamps, self.masks, self.reasons, self.max_mhz = [], [], [], [], set(), None
-        self.window = [None, None]
+        self.window = [None, None, None]
         self._stop_evt = threading.Event()
         try:
             import pynvml
@@ -109,15 +109,22 @@ class ClockSampler(threading.Thread):
             self._stop_evt.wait(self.period)
 
     def mark(self, which: int) -> None:
-        """Start (0) or end (1) of the timed region; the summary covers the samples between the two."""
+        """Start (0) or end (1) of the timed region, start of its warm-up (2); the summary covers the
+        samples between 0 and 1, or, when those are fewer than three, between 2 and 1."""
         self.window[which] = time.perf_counter()
 
     def stop(self) -> dict:
         self._stop_evt.set()
         self.join(timeout=2)
-        t0, t1 = self.window
-        keep = [i for i, t in enumerate(self.stamps) if (t0 is None or t >= t0) and (t1 is None or t <= t1)]
-        if len(keep) < 3:  # a region shorter than a few sampling periods: everything since the warm-up began
+        t0, t1, tw = self.window
+
+        def between(lo, hi):
+            return [i for i, t in enumerate(self.stamps) if (lo is None or t >= lo) and (hi is None or t <= hi)]
+
+        keep = between(t0, t1)
+        if len(keep) < 3:  # a region shorter than a few sampling periods: the warm-up steps (same work) count too
+            keep = between(tw, t1)
+        if len(keep) < 3:
             keep = list(range(len(self.stamps)))
         clocks = [self.samples[i] for i in keep]
         power = [self.power[i] for i in keep]
@@ -400,6 +407,10 @@ def run(args):
 
 
 def _measure(args, arm, rank, world, dev):
+    # The sampler starts before the inputs are made: the first NVML queries of a process take tens of
+    # milliseconds (eight ranks initialise the library at once), longer than a whole timed region at 8 GPUs.
+    sampler = ClockSampler(dev.index, period_s=0.002)
+    sampler.start()
     host, d = make_inputs(rank, world, dev)
     flush = L2Flush(dev)
     align = torch.zeros(1, device=dev)
@@ -484,6 +495,8 @@ def _measure(args, arm, rank, world, dev):
         return out
 
     def measure(e2e: bool, sampler=None):
+        if sampler is not None:
+            sampler.mark(2)
         for _ in range(args.warmup):
             step(None, e2e)
         torch.cuda.synchronize()
@@ -504,8 +517,6 @@ def _measure(args, arm, rank, world, dev):
             sampler.mark(1)
         return reduce_times(events), arm.launches() - before, wall
 
-    sampler = ClockSampler(dev.index, period_s=0.002)
-    sampler.start()
     per_call, launches, wall = measure(e2e=False, sampler=sampler)
     clocks = sampler.stop()
     e2e_calls, _, _ = measure(e2e=True)

@@ -50,6 +50,24 @@ def test_clock_sampler_reads_only_and_reports_the_loaded_median(monkeypatch):
         "nvmlDeviceGetCurrentClocksEventReasons"}
 
 
+def test_clock_sampler_window_falls_back_to_the_warm_up(monkeypatch):
+    """A timed region shorter than three sampling periods is summarised together with
+    its warm-up steps, not with whatever ran since the sampler started."""
+    import bench
+
+    fake = _fake_nvml([1965] * 10 + [1300] * 500, [150_000] * 10 + [900_000] * 500, 0x4)
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    s = bench.ClockSampler(0, period_s=0.002)
+    s.start()
+    time.sleep(0.06)           # set-up: idle samples at the maximum clock
+    s.mark(2)
+    time.sleep(0.05)           # warm-up
+    s.mark(0)
+    s.mark(1)                  # a timed region without a single sample
+    out = s.stop()
+    assert out["samples"] >= 3 and out["sm_mhz_all_samples_median"] == 1300   # no idle sample in the summary
+
+
 def test_clock_sampler_without_nvml(monkeypatch):
     import bench
 
