@@ -842,6 +842,16 @@ int fill_params(const KbA2aArgs* a, A2aParams* p, int sms) {
   return KB_OK;
 }
 
+// Function attributes and occupancy belong to a device's context, and a process may
+// use several devices in its life (a pool worker that serves rank 3 in one case and
+// rank 5 in the next): everything cached about a kernel is cached per device.
+constexpr int MAX_DEVICES = 64;
+int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -1;
+  return dev;
+}
+
 int device_sms(int* sms) {
   static int cached[64] = {0};
   int dev = 0;
@@ -886,10 +896,11 @@ extern "C" int kb_a2a_dispatch(const KbA2aArgs* a, void* stream) {
   rc = fill_params(a, &p, sms);
   if (rc != KB_OK) return rc;
   const size_t smem = dispatch_smem_bytes(p.E);
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[MAX_DEVICES] = {};
+  const int slot = current_device_slot();
+  if (slot < 0 || !attr_set[slot]) {
     KB_CUDA_OK(cudaFuncSetAttribute(a2a_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dispatch_smem_bytes(MAX_EXPERTS)));
-    attr_set = true;
+    if (slot >= 0) attr_set[slot] = true;
   }
   a2a_dispatch_kernel<<<p.tok_groups * p.h_splits, A2A_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p);
   KB_CUDA_OK(cudaGetLastError());
@@ -962,20 +973,25 @@ static int launch_fused(const A2aParams& p, int sms, cudaStream_t st) {
     }
   }
   const size_t smem = dispatch_smem_bytes(p.E);  // the combine phase reuses the slot table at the front of it
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[MAX_DEVICES] = {};
+  const int slot = current_device_slot();
+  if (slot < 0 || !attr_set[slot]) {
     KB_CUDA_OK(cudaFuncSetAttribute(a2a_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dispatch_smem_bytes(MAX_EXPERTS)));
-    attr_set = true;
+    if (slot >= 0) attr_set[slot] = true;
   }
   // The occupancy query costs microseconds of host time; its answer depends only
-  // on the kernel instance and the shared-memory size.
-  static size_t cached_smem = ~size_t(0);
-  static int cached_per_sm = 0;
-  int per_sm = cached_per_sm;
-  if (cached_smem != smem) {
+  // on the device, the kernel instance and the shared-memory size.
+  static size_t cached_smem[MAX_DEVICES];
+  static int cached_per_sm[MAX_DEVICES] = {};
+  int per_sm = 0;
+  if (slot >= 0 && cached_per_sm[slot] > 0 && cached_smem[slot] == smem) {
+    per_sm = cached_per_sm[slot];
+  } else {
     KB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, a2a_fused_kernel<T>, A2A_THREADS, smem));
-    cached_smem = smem;
-    cached_per_sm = per_sm;
+    if (slot >= 0) {
+      cached_smem[slot] = smem;
+      cached_per_sm[slot] = per_sm;
+    }
   }
   const int units = p.tok_groups * p.h_splits + 1;  // data CTAs and the poller
   if (per_sm < 1 || units > per_sm * sms) {
@@ -993,8 +1009,13 @@ static int launch_fused(const A2aParams& p, int sms, cudaStream_t st) {
 // they themselves have been served by this rank: all of them must be resident.
 template <typename T>
 static int launch_ll(const A2aParams& p, int sms, cudaStream_t st) {
-  static int per_sm = 0;
-  if (per_sm == 0) KB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, a2a_ll_kernel<T>, A2A_THREADS, 0));
+  static int cached_per_sm[MAX_DEVICES] = {};
+  const int slot = current_device_slot();
+  int per_sm = slot >= 0 ? cached_per_sm[slot] : 0;
+  if (per_sm == 0) {
+    KB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, a2a_ll_kernel<T>, A2A_THREADS, 0));
+    if (slot >= 0) cached_per_sm[slot] = per_sm;
+  }
   const int units = p.tok_groups * p.h_splits;
   if (per_sm < 1 || units > per_sm * sms) {
     kb::set_error("a2a low-latency: %d CTAs cannot be co-resident (%d per SM)", units, per_sm);

@@ -378,3 +378,43 @@ def test_departed_rank_is_seen_on_the_host_before_the_next_launch(monkeypatch):
     # no multicast anywhere in a test where a rank stops taking part: neither in NCCL nor in the heap
     res = run_ranks(_rank_leaves, world, backend="nccl", timeout=120, env={"NCCL_NVLS_ENABLE": "0", "KB200_NVLS": "0"})
     assert all(gone == [world - 1] for gone in res)
+
+
+def _two_devices_one_process(rank, world):
+    """The same process runs the one-launch MoE kernel (more than 48 KB of dynamic
+    shared memory: a per-device function attribute) and a GEMM first on one device,
+    then on another, as an evaluator's pool worker does when it serves rank 0 in
+    one case and rank 1 in the next."""
+    import torch
+
+    from kernel_b200.ops.dispatch_combine import MoEAllToAll
+    from kernel_b200.ops.gemm import gemm
+
+    res = []
+    for index in (0, 1):
+        dev = torch.device("cuda", index)
+        torch.cuda.set_device(dev)
+        g = torch.Generator(device=dev).manual_seed(3)
+        E, k, H, T = 64, 4, 4096, 100          # above the low-latency limit: the regular one-launch kernel
+        x = torch.randn(T, H, device=dev, generator=g).to(torch.float16)
+        idx = torch.rand(T, E, device=dev, generator=g).argsort(1)[:, :k].to(torch.int32).contiguous()
+        w = torch.rand(T, k, device=dev, generator=g)
+        ctx = MoEAllToAll(E, k, H, 128, dtype=torch.float16, device=dev)
+        out = ctx.dispatch_scale_combine(x, idx, w, 0)
+        torch.cuda.synchronize(dev)
+        ctx.heap.check_status()
+        want = x.float() * w.sum(-1, keepdim=True)
+        ok_a2a = bool(torch.allclose(out.float(), want, rtol=1e-2, atol=5e-3))
+        ctx.heap.close()
+        a = torch.randn(512, 1024, device=dev, generator=g).to(torch.bfloat16)
+        b = (torch.randn(768, 1024, device=dev, generator=g) / 32).to(torch.bfloat16)
+        c = gemm(a, b)
+        torch.cuda.synchronize(dev)
+        ok_gemm = bool(torch.allclose(c.float(), a.float() @ b.float().t(), rtol=2e-2, atol=2e-2))
+        res.append((ok_a2a, ok_gemm))
+    return res
+
+
+def test_one_process_uses_the_kernels_on_two_devices_in_turn():
+    (res,) = run_ranks(_two_devices_one_process, 1, backend="nccl", timeout=300)
+    assert res == [(True, True), (True, True)]
