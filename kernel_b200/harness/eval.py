@@ -427,34 +427,44 @@ def run_profile(cfg: RunConfig, test: TestCase, rank: int) -> str:
 
 # --------------------------------------------------------------- pool front ----
 class WorkerPool:
-    """The spawn pool of the per-rank workers, replaceable after a time-out.
+    """One spawned worker process per rank slot, replaceable after a time-out.
+
+    Rank r of every case runs in worker r, hence on GPU r for the whole run: one
+    process per GPU, one CUDA context per process.  (The reference's evaluator
+    gives a case's ranks to whichever workers of one shared pool are free,
+    ``eval.py:201``, so a worker changes GPU between cases and ends up with a
+    context, an allocator pool and per-device kernel attributes on several.)
 
     A case that ran into its time limit leaves its workers running: they hold the
     rendezvous, their GPUs and possibly a device-side wait, and the next case would
-    be queued behind them (the reference's evaluator has the same weakness,
-    ``eval.py:201``).  ``rebuild`` terminates those processes and starts fresh ones."""
+    be queued behind them (the reference's evaluator has the same weakness).
+    ``rebuild`` terminates those processes and starts fresh ones."""
 
     def __init__(self, n_workers: int):
         self.n_workers = n_workers
         self._ctx = multiprocessing.get_context("spawn")
-        self.pool = self._ctx.Pool(n_workers)
+        self.pools = [self._ctx.Pool(1) for _ in range(n_workers)]
         self.rebuilds = 0
 
+    def _stop(self) -> None:
+        for p in self.pools:
+            p.terminate()
+        for p in self.pools:
+            p.join()
+
     def rebuild(self) -> None:
-        self.pool.terminate()
-        self.pool.join()
-        self.pool = self._ctx.Pool(self.n_workers)
+        self._stop()
+        self.pools = [self._ctx.Pool(1) for _ in range(self.n_workers)]
         self.rebuilds += 1
 
-    def apply(self, fn, args):
-        return self.pool.apply(fn, args)
+    def apply(self, fn, args, slot: int = 0):
+        return self.pools[slot % self.n_workers].apply(fn, args)
 
-    def apply_async(self, fn, args):
-        return self.pool.apply_async(fn, args)
+    def apply_async(self, fn, args, slot: int = 0):
+        return self.pools[slot % self.n_workers].apply_async(fn, args)
 
     def close(self) -> None:
-        self.pool.terminate()
-        self.pool.join()
+        self._stop()
 
     def __enter__(self):
         return self
@@ -523,7 +533,7 @@ class Runner:
         if world is None:
             res = self.pool.apply(run_local_test, (cfg, test))
             return (False, str(res)) if isinstance(res, WorkerFailure) else res
-        pending = [self.pool.apply_async(run_distributed_test, (cfg, test, r)) for r in range(world)]
+        pending = [self.pool.apply_async(run_distributed_test, (cfg, test, r), r) for r in range(world)]
         results = [(False, str(r)) if isinstance(r, WorkerFailure) else r for r in self._collect(pending, TEST_TIMEOUT_S)]
         ok = all(r[0] for r in results)
         errors = "\n".join(f"rank {i} - {r[1]}" for i, r in enumerate(results) if not r[0])
@@ -538,7 +548,7 @@ class Runner:
         if world is None:
             res = self.pool.apply(run_local_benchmark, (cfg, test, recheck, max_repeats, max_time_ns))
             return str(res) if isinstance(res, WorkerFailure) else res
-        pending = [self.pool.apply_async(run_distributed_benchmark, (cfg, test, r, recheck, max_repeats, max_time_ns))
+        pending = [self.pool.apply_async(run_distributed_benchmark, (cfg, test, r, recheck, max_repeats, max_time_ns), r)
                    for r in range(world)]
         results = self._collect(pending, BENCH_TIMEOUT_S)
         failed = [(i, r) for i, r in enumerate(results) if not isinstance(r, Stats)]
@@ -551,7 +561,7 @@ class Runner:
         cfg = self._cfg(test)
         if world is None:
             return str(self.pool.apply(run_profile, (cfg, test, 0)))
-        pending = [self.pool.apply_async(run_profile, (cfg, test, r)) for r in range(world)]
+        pending = [self.pool.apply_async(run_profile, (cfg, test, r), r) for r in range(world)]
         return str(self._collect(pending, BENCH_TIMEOUT_S)[0])
 
 

@@ -238,3 +238,26 @@ def test_sigterm_takes_the_workers_along(tmp_path):
         if proc.poll() is None:
             proc.kill()
         os.close(r)
+
+
+def test_a_rank_keeps_its_worker_process_from_case_to_case(tmp_path):
+    """Rank r of every case runs in worker r (one process per GPU for the whole run)."""
+    (tmp_path / "pid_sub.py").write_text(
+        "import os\n"
+        "import torch.distributed as dist\n"
+        "from kernel_b200.tasks.gemm_rs.submission import custom_kernel as good\n"
+        "def custom_kernel(data):\n"
+        "    with open(os.environ['PID_LOG'], 'a') as f:\n"
+        "        f.write(f'{dist.get_rank()} {os.getpid()}\\n')\n"
+        "    return good(data)\n")
+    log_path = tmp_path / "pids.txt"
+    cases = "\n".join(f"world_size: 2; m: 64; n: 128; k: 256; has_bias: False; seed: {s}" for s in (3, 4, 5)) + "\n"
+    rc, log, err = _run(["test", "@tests", "--backend", "gloo", "--submission", "pid_sub"], cases, tmp_path,
+                        env_extra={"PYTHONPATH": f"{ROOT}:{tmp_path}", "PID_LOG": str(log_path)})
+    assert rc == 0, err
+    pids = {0: set(), 1: set()}
+    for line in log_path.read_text().split("\n"):
+        if line:
+            r, pid = line.split()
+            pids[int(r)].add(pid)
+    assert len(pids[0]) == 1 and len(pids[1]) == 1 and pids[0] != pids[1]
