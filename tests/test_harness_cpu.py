@@ -261,3 +261,30 @@ def test_a_rank_keeps_its_worker_process_from_case_to_case(tmp_path):
             r, pid = line.split()
             pids[int(r)].add(pid)
     assert len(pids[0]) == 1 and len(pids[1]) == 1 and pids[0] != pids[1]
+
+
+def test_benchmark_mode_reports_a_raising_rank_as_text(tmp_path):
+    """Same as the test-mode case above, through the timed loop: the rank that raises
+    leaves the others in the loop's barrier; the case is reported as failed with the
+    error's text and the evaluator does not wait for its full time limit."""
+    import time
+
+    (tmp_path / "raising_sub2.py").write_text(
+        "import torch.distributed as dist\n"
+        "from kernel_b200 import _native as N\n"
+        "from kernel_b200.tasks.gemm_rs.submission import custom_kernel as good\n"
+        "calls = 0\n"
+        "def custom_kernel(data):\n"
+        "    global calls\n"
+        "    calls += 1\n"
+        "    if calls >= 3 and dist.get_rank() == 1:\n"
+        "        raise N.SymmTimeoutError(N.KB_ERR_TIMEOUT, 'made up for the test')\n"
+        "    return good(data)\n")
+    t0 = time.monotonic()
+    rc, log, err = _run(["benchmark", "@tests", "--backend", "gloo", "--submission", "raising_sub2"], RS + "\n", tmp_path,
+                        env_extra={"PYTHONPATH": f"{ROOT}:{tmp_path}", "KB200_EVAL_BENCH_TIMEOUT_S": "300",
+                                   "KB200_EVAL_FAIL_GRACE_S": "5", "KB200_WAIT_LIMIT_MS": "3000"})
+    assert time.monotonic() - t0 < 200
+    report = "\n".join(f"{k}: {v}" for k, v in log.items())
+    assert rc == 112 and log["check"] == "fail"
+    assert "SymmTimeoutError" in report and "made up for the test" in report
