@@ -147,6 +147,7 @@ def _declare(lib: C.CDLL) -> None:
         "kb_a2a_combine": (i, [C.POINTER(A2aArgs), vp]),
         "kb_a2a_round_trip": (i, [C.POINTER(A2aArgs), vp]),
         "kb_a2a_round_trip_host": (i, [C.POINTER(A2aArgs), i]),
+        "kb_a2a_round_trip_host_ll": (i, [C.POINTER(A2aArgs), i]),
         "kb_a2a_dispatch_host": (i, [C.POINTER(A2aArgs), i]),
         "kb_a2a_combine_host": (i, [C.POINTER(A2aArgs), i]),
         "kb_gemm_host": (i, [C.POINTER(GemmArgs), i]),

@@ -27,6 +27,7 @@ SOURCES = [
     "symm/fd_exchange.cpp",
     "symm/symm_heap.cpp",
     "symm/a2a_host.cpp",
+    "symm/a2a_ll_host.cpp",
     "symm/gemm_host.cpp",
     "kernels/a2a.cu",
     "kernels/gemm_sm100.cu",

@@ -180,6 +180,8 @@ int kb_a2a_combine(const KbA2aArgs* a, void* stream);
 // the rank that never arrived.  The dispatch and combine phases are also callable
 // on their own, around an expert computation of the caller.
 int kb_a2a_round_trip_host(const KbA2aArgs* a, int timeout_ms);
+// The low-latency protocol (flags inside the data, landing areas at a->ll_off) for CPU ranks.
+int kb_a2a_round_trip_host_ll(const KbA2aArgs* a, int timeout_ms);
 int kb_a2a_dispatch_host(const KbA2aArgs* a, int timeout_ms);
 int kb_a2a_combine_host(const KbA2aArgs* a, int timeout_ms);
 // dispatch + simulated expert + combine in ONE cooperative launch.

@@ -77,7 +77,7 @@ class MoEAllToAll:
             meta_bytes = int(lib.kb_a2a_meta_bytes(self.world, max_num_tokens, experts_per_token))
             # small contexts get the landing areas of the low-latency round trip (flags inside the data)
             ll_bytes = 0
-            if self.native and os.environ.get("KB200_A2A_LL", "1") == "1":
+            if os.environ.get("KB200_A2A_LL", "1") == "1":  # CPU ranks run the same protocol (a2a_ll_host.cpp)
                 ll_bytes = int(lib.kb_a2a_ll_bytes(self.world, max_num_tokens, experts_per_token, hidden_dim, eb))
             need = 2 * rows + counts + flag_bytes + sync_bytes + meta_bytes + ll_bytes + 8192
             # no multicast mapping here: these kernels use peer loads and stores only
@@ -173,7 +173,8 @@ class MoEAllToAll:
                 out = torch.empty_like(x)
                 self.epoch += 1
                 a = self._args(x, indices, weights, out, scale_mode)
-                N.check(self._lib.kb_a2a_round_trip_host(C.byref(a), max(1, _WAIT_LIMIT_NS // 1_000_000)))
+                fn = self._lib.kb_a2a_round_trip_host_ll if self.ll_off else self._lib.kb_a2a_round_trip_host
+                N.check(fn(C.byref(a), max(1, _WAIT_LIMIT_NS // 1_000_000)))
                 return out
             return self._cpu_round_trip(x, indices, weights, scale_mode)
         global launch_count
