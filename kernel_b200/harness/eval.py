@@ -11,7 +11,13 @@ What differs from the reference, on purpose:
 
 * times are device times: a CUDA event pair around ``custom_kernel`` alone on
   every rank, MAX over ranks (the reference times rank 0's wall clock around the
-  input clone too, ``eval.py:354-367``);
+  input clone too, ``eval.py:354-367``); on GPUs a one-element all-reduce queued
+  right before the start event lets the devices begin together, so the hosts'
+  skew after the barrier is not timed as waiting inside the early ranks' kernels;
+* rank r of every case runs in worker process r (one process per GPU for the
+  whole run; the reference hands ranks to whichever pool workers are free,
+  ``eval.py:201``), a worker's error comes back as text, a failed rank shortens
+  the wait for its peers, and SIGTERM terminates the workers;
 * the any-rank-failed flag is an all-reduce, so no rank is left behind in a
   broadcast when another rank fails (``eval.py:376-400``);
 * the rendezvous port is a free port unless ``MASTER_PORT`` is set, the
@@ -330,6 +336,7 @@ def run_distributed_benchmark(cfg: RunConfig, test: TestCase, rank: int, recheck
         if _any_failed(not good, dev):
             return message or "a peer rank failed the correctness check"
         durations: List[float] = []
+        align = torch.zeros(1, device=dev)
         t_begin = time.perf_counter_ns()
         for i in range(max_repeats):
             if recheck:
@@ -340,6 +347,12 @@ def run_distributed_benchmark(cfg: RunConfig, test: TestCase, rank: int, recheck
             clear_l2_cache(dev if dev.type == "cuda" else None)
             _sync(dev)
             dist.barrier()
+            if dev.type == "cuda":
+                # The hosts leave the barrier tens of microseconds apart.  A small all-reduce queued on the
+                # stream right before the start event makes the GPUs begin together: every rank's kernel is
+                # in its queue by the time the slowest host has joined, so the skew of the hosts does not
+                # end up inside the early ranks' kernels as waiting time.
+                dist.all_reduce(align)
             out, ns = _timed_call(lambda: sub.custom_kernel(work), dev)
             t = torch.tensor([ns], dtype=torch.float64, device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
