@@ -17,7 +17,8 @@ What differs from the reference, on purpose:
 * rank r of every case runs in worker process r (one process per GPU for the
   whole run; the reference hands ranks to whichever pool workers are free,
   ``eval.py:201``), a worker's error comes back as text, a failed rank shortens
-  the wait for its peers, and SIGTERM terminates the workers;
+  the wait for its peers, and workers that are replaced or stopped free their
+  workspaces locally before they exit (``_worker_stop``);
 * the any-rank-failed flag is an all-reduce, so no rank is left behind in a
   broadcast when another rank fails (``eval.py:376-400``);
 * the rendezvous port is a free port unless ``MASTER_PORT`` is set, the
@@ -208,10 +209,62 @@ def _reports_errors(fn):
     def guarded(*args, **kwargs):
         try:
             return fn(*args, **kwargs)
+        except (SystemExit, KeyboardInterrupt):
+            raise  # the worker has been told to stop
         except BaseException as e:  # noqa: BLE001 - the text goes back to the evaluator
             return WorkerFailure(f"{type(e).__name__}: {e}")
 
     return guarded
+
+
+KILL_GRACE_S = float(os.environ.get("KB200_EVAL_KILL_GRACE_S", "20"))
+_SUBMISSION_MODULES = ("all2all", "gemm_rs", "ag_gemm")
+
+
+def _release_workspaces_locally(settle_s: float) -> int:
+    """Frees every cached workspace of this process without waiting for any peer:
+    waits for this rank's own kernels (their waits are time-bounded), gives the
+    peers' kernels ``settle_s`` to finish with this rank's memory, then unbinds
+    and unmaps.  Returns the number of workspaces freed."""
+    mods = [sys.modules.get(f"kernel_b200.tasks.{t}.submission") for t in _SUBMISSION_MODULES]
+    held = [m for m in mods if m is not None and getattr(m, "_contexts", None)]
+    n = sum(len(m._contexts) for m in held)
+    if n == 0:
+        return 0
+    try:
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        time.sleep(settle_s)
+    except Exception:
+        pass
+    for m in held:
+        try:
+            m.release_contexts(collective=False)
+        except Exception:
+            pass
+    return n
+
+
+def _worker_stop(signum, frame):
+    """SIGTERM in a worker: the evaluator is replacing its pool (a case ran out of
+    time) or leaving.  A process that dies while its memory is bound to a multicast
+    object, or mapped by a peer that is still inside a kernel, can fault the peers'
+    GPUs; so the worker leaves in order: own kernels done, a pause for the peers'
+    (all workers get the signal together and all kernel waits are bounded), then
+    unbind and unmap.  A worker stuck inside a library call never gets here; the
+    evaluator kills it after ``KB200_EVAL_KILL_GRACE_S``, by which time its peers have
+    left the shared memory alone."""
+    signal.signal(signal.SIGTERM, signal.SIG_DFL)
+    freed = _release_workspaces_locally(settle_s=float(os.environ.get("KB200_EVAL_SETTLE_S", "3")))
+    trace = os.environ.get("KB200_EVAL_LIFECYCLE_LOG")
+    if trace:
+        with open(trace, "a") as f:
+            f.write(f"{os.getpid()} stopped in order, {freed} workspace(s) freed\n")
+    raise SystemExit(128 + signum)
+
+
+def _worker_init() -> None:
+    signal.signal(signal.SIGTERM, _worker_stop)
 
 
 def _raise_fd_limit() -> None:
@@ -253,6 +306,8 @@ class _Group:
     def __exit__(self, exc_type, exc, tb):
         import torch.distributed as dist
 
+        if exc_type is not None and issubclass(exc_type, (SystemExit, KeyboardInterrupt)):
+            return False  # the process is leaving: no collective of any kind
         try:
             if exc_type is None:
                 # the evaluated module, then the built-in submissions a user module may wrap
@@ -456,10 +511,22 @@ class WorkerPool:
     def __init__(self, n_workers: int):
         self.n_workers = n_workers
         self._ctx = multiprocessing.get_context("spawn")
-        self.pools = [self._ctx.Pool(1) for _ in range(n_workers)]
+        self.pools = [self._ctx.Pool(1, initializer=_worker_init) for _ in range(n_workers)]
         self.rebuilds = 0
 
     def _stop(self) -> None:
+        """SIGTERM to every worker at once (they leave in order, see ``_worker_stop``),
+        SIGKILL for those that have not left after ``KB200_EVAL_KILL_GRACE_S``."""
+        procs = [w for p in self.pools for w in list(getattr(p, "_pool", []))]
+        for w in procs:
+            if w.is_alive():
+                w.terminate()
+        t_end = time.monotonic() + KILL_GRACE_S
+        while any(w.is_alive() for w in procs) and time.monotonic() < t_end:
+            time.sleep(0.05)
+        for w in procs:
+            if w.is_alive():
+                w.kill()
         for p in self.pools:
             p.terminate()
         for p in self.pools:
@@ -467,7 +534,7 @@ class WorkerPool:
 
     def rebuild(self) -> None:
         self._stop()
-        self.pools = [self._ctx.Pool(1) for _ in range(self.n_workers)]
+        self.pools = [self._ctx.Pool(1, initializer=_worker_init) for _ in range(self.n_workers)]
         self.rebuilds += 1
 
     def apply(self, fn, args, slot: int = 0):

@@ -31,11 +31,12 @@ def get_context(M: int, K: int, device: torch.device) -> AGGemm:
     return ctx
 
 
-def release_contexts() -> None:
+def release_contexts(collective: bool = True) -> None:
     """Frees cached workspaces.  Collective for the contexts of the current process
     group (call before destroying it); contexts left over from an earlier group
-    are freed locally."""
-    current = _group()
+    are freed locally.  ``collective=False`` frees everything locally (a process that
+    is leaving while its peers may be gone)."""
+    current = _group() if collective else object()
     for ctx in _contexts.values():
         for sub, _ in getattr(ctx, "_stream_state", {}).values():  # chunk-sized contexts of run_from_host
             if sub is not ctx and sub.heap is not None:

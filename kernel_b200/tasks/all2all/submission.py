@@ -36,11 +36,12 @@ def get_context(cfg, world_size: int, device: torch.device) -> MoEAllToAll:
     return ctx
 
 
-def release_contexts() -> None:
+def release_contexts(collective: bool = True) -> None:
     """Frees cached workspaces.  Collective for the contexts of the current process
     group (call before destroying it); contexts left over from an earlier group
-    are freed locally."""
-    current = _group()
+    are freed locally.  ``collective=False`` frees everything locally (a process that
+    is leaving while its peers may be gone)."""
+    current = _group() if collective else object()
     for ctx in _contexts.values():
         if ctx.heap is not None:
             ctx.heap.close(collective=ctx.process_group is current)

@@ -288,3 +288,28 @@ def test_benchmark_mode_reports_a_raising_rank_as_text(tmp_path):
     report = "\n".join(f"{k}: {v}" for k, v in log.items())
     assert rc == 112 and log["check"] == "fail"
     assert "SymmTimeoutError" in report and "made up for the test" in report
+
+
+def test_replaced_workers_free_their_workspaces_before_they_leave(tmp_path):
+    """Rank 1 holds a workspace and never returns.  When the case runs out of time the
+    evaluator sends SIGTERM to all workers; the one that can still run Python frees
+    its workspace locally (no collective) before it exits, the one blocked inside a
+    collective is killed after the grace period; the next case runs in fresh workers."""
+    (tmp_path / "holding_sub.py").write_text(
+        "import time\n"
+        "import torch.distributed as dist\n"
+        "from kernel_b200.tasks.gemm_rs.submission import custom_kernel as good\n"
+        "def custom_kernel(data):\n"
+        "    out = good(data)\n"
+        "    if data[0].shape[0] == 128 and dist.get_rank() == 1:\n"
+        "        time.sleep(600)\n"
+        "    return out\n")
+    log_path = tmp_path / "lifecycle.txt"
+    stuck = "world_size: 2; m: 128; n: 128; k: 256; has_bias: False; seed: 3"
+    rc, log, err = _run(["test", "@tests", "--backend", "gloo", "--submission", "holding_sub"], stuck + "\n" + RS + "\n", tmp_path,
+                        env_extra={"PYTHONPATH": f"{ROOT}:{tmp_path}", "KB200_EVAL_TEST_TIMEOUT_S": "15",
+                                   "KB200_EVAL_KILL_GRACE_S": "6", "KB200_EVAL_SETTLE_S": "0.2",
+                                   "KB200_EVAL_LIFECYCLE_LOG": str(log_path), "KB200_WAIT_LIMIT_MS": "3000"})
+    assert rc == 112 and log["test.0.status"] == "fail" and "timed out" in log["test.0.error"]
+    assert log["test.1.status"] == "pass"
+    assert "1 workspace(s) freed" in log_path.read_text()
