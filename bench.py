@@ -40,6 +40,7 @@ import argparse
 import json
 import math
 import os
+import signal
 import socket
 import sys
 import threading
@@ -375,7 +376,16 @@ class ReferenceArm:
 
 
 # ------------------------------------------------------------------ timing ----
+def _stop_in_order(signum, frame):
+    # A launcher's or a caller's time limit arrives as SIGTERM: leave through the handler of
+    # run() below, which waits for this rank's kernels and unbinds the workspaces, instead of
+    # dying with memory bound to a multicast object that the other ranks still use.
+    signal.signal(signal.SIGTERM, signal.SIG_DFL)
+    raise SystemExit(128 + signum)
+
+
 def run(args):
+    signal.signal(signal.SIGTERM, _stop_in_order)
     rank, world, dev = init_dist(args.gpus)
     try:
         arm = OursArm(rank, world, dev) if args.impl == "ours" else ReferenceArm(rank, world, dev)
