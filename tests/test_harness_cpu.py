@@ -154,7 +154,8 @@ def test_a_case_that_runs_out_of_time_does_not_block_the_next_one(tmp_path):
         "    return good(data)\n")
     stuck = "world_size: 2; m: 128; n: 128; k: 256; has_bias: False; seed: 3"
     rc, log, err = _run(["test", "@tests", "--backend", "gloo", "--submission", "stuck_sub"], stuck + "\n" + RS + "\n", tmp_path,
-                        env_extra={"PYTHONPATH": f"{ROOT}:{tmp_path}", "KB200_EVAL_TEST_TIMEOUT_S": "20",
+                        env_extra={"PYTHONPATH": f"{ROOT}:{tmp_path}", "KB200_EVAL_TEST_TIMEOUT_S": "15",
+                                   "KB200_EVAL_KILL_GRACE_S": "5", "KB200_EVAL_SETTLE_S": "0.2",
                                    "KB200_WAIT_LIMIT_MS": "3000"})
     assert rc == 112 and log["check"] == "fail"
     assert log["test.0.status"] == "fail" and "timed out" in log["test.0.error"]
