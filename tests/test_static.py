@@ -46,6 +46,19 @@ def test_every_wait_is_bounded():
 
 
 @pytest.mark.skipif(shutil.which("nvcc") is None and not Path("/usr/local/cuda/bin/nvcc").exists(), reason="no nvcc")
+def test_kernel_attributes_and_occupancy_are_cached_per_device():
+    """A function attribute (dynamic shared memory above 48 KB) and an occupancy
+    figure belong to a device's context.  A process may use several devices in its
+    life, so a launcher that remembers them must remember them per device: no
+    scalar "done once" flag next to ``cudaFuncSetAttribute`` or an occupancy query."""
+    for p in _sources():
+        text = p.read_text()
+        if "cudaFuncSetAttribute" not in text and "cudaOccupancyMaxActiveBlocksPerMultiprocessor" not in text:
+            continue
+        scalars = re.findall(r"static\s+(?:bool|int|size_t)\s+(?:attr_set|cached_\w+|per_sm)\s*(?:=[^;\[]*)?;", text)
+        assert not scalars, f"{p.name}: per-process cache of a per-device property: {scalars}"
+
+
 def test_build_for_sm100a_and_load():
     from kernel_b200 import _native
     from kernel_b200.csrc import build
