@@ -1,8 +1,11 @@
-"""Every routing of tiny MoE cases through the host-heap protocol, against the
-closed form ``out[t] = x[t] * sum_k w[t,k] * scale(expert(t,k))``: the slot
-arithmetic has no untested combination at these sizes."""
+"""Every routing of tiny MoE cases through both host-heap protocols (rows grouped
+by expert with flag hand-offs; one row per destination rank with the flags inside
+the data), against the closed form ``out[t] = x[t] * sum_k w[t,k] *
+scale(expert(t,k))``: the slot arithmetic has no untested combination at these
+sizes."""
 import itertools
 
+import pytest
 import torch
 
 from _mp import run_ranks
@@ -35,12 +38,14 @@ def _exhaustive(rank, world, E, k, T):
     return bad, len(combos)
 
 
-def test_all_routings_two_ranks_two_tokens():
+@pytest.mark.parametrize("low_latency", ["0", "1"])
+def test_all_routings_two_ranks_two_tokens(low_latency):
     for E, k in ((2, 1), (2, 2), (4, 1), (4, 2)):
-        for bad, n in run_ranks(_exhaustive, 2, E, k, 2):
+        for bad, n in run_ranks(_exhaustive, 2, E, k, 2, env={"KB200_A2A_LL": low_latency}):
             assert bad == 0, (E, k, bad, n)
 
 
-def test_all_routings_three_ranks_one_token():
-    for bad, n in run_ranks(_exhaustive, 3, 6, 2, 1):
+@pytest.mark.parametrize("low_latency", ["0", "1"])
+def test_all_routings_three_ranks_one_token(low_latency):
+    for bad, n in run_ranks(_exhaustive, 3, 6, 2, 1, env={"KB200_A2A_LL": low_latency}):
         assert bad == 0 and n == 30
